@@ -7,7 +7,9 @@
  *
  * Families: "Nekodra" (config.json + model.safetensors: parallel layers of latent attention without positions and a
  * routed feed-forward with identity experts), "Musilorn" (sandwich-normed layers of convolved, capped attention with a
- * sink or of retention with a carried state, a span of layers run several times), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
+ * sink or of retention with a carried state, a span of layers run several times), "Tomalix" (pre-norm layers of
+ * differential attention, of chunk-masked gated attention beside a selective scan, or of plain attention with ramped
+ * frequency interpolation; dense or routed squared-relu feed-forwards; a repeated span of layers), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
  * a config.json naming the b200_model_config fields).
  */
 #ifndef B200_SERVE_H
@@ -43,6 +45,7 @@ int b200_layernorm_pair(const float* x, const int* rows, int n_rows, int width, 
 #define B200_GG_SIGMOID_MUL 1 /* C = acc * sigmoid(aux[row, col])                                   */
 #define B200_GG_GLU 2         /* C = silu(A W[0:N]^T) * (A W[N:2N]^T); W has 2N rows; trans_b only  */
 #define B200_GG_GLU_GELU 3    /* the same with gelu in its tanh form as the activation              */
+#define B200_GG_RELU2 4       /* C = max(acc, 0)^2                                                   */
 
 typedef struct b200_gemm_grouped_args {
     const void* A; const void* W; void* C;
@@ -60,8 +63,8 @@ typedef struct b200_gemm_grouped_args {
 } b200_gemm_grouped_args;
 int b200_gemm_grouped(const b200_gemm_grouped_args* args, void* stream);
 
-/* y[n_tokens, N] = x[n_tokens, K] W[N, K]^T for contiguous operands (epi B200_GG_NONE), or the GLU form with W [2N, K]
- * (B200_GG_GLU). bfloat16 operands run on the tcgen05 / TMEM GEMM of the LLaMA path (weights streamed once through the
+/* y[n_tokens, N] = x[n_tokens, K] W[N, K]^T for contiguous operands (epi B200_GG_NONE, or B200_GG_RELU2 on every
+ * output), or the GLU form with W [2N, K] (B200_GG_GLU, B200_GG_GLU_GELU). bfloat16 operands run on the tcgen05 / TMEM GEMM of the LLaMA path (weights streamed once through the
  * M axis up to 256 token rows, tokens on the M axis above; fp32 accumulation; out_dtype B200_BF16 or B200_F32) when the
  * shape allows (K % 8 == 0, 16-byte aligned pointers, GLU: N % 128 == 0); everything else, and B200_F32 operands, goes
  * to b200_gemm_grouped. workspace: split-K partials of the weight-streaming mode (may be NULL: single split). */
@@ -95,6 +98,10 @@ int b200_latent_attention(const float* qa, float* out, const void* pool, const i
  * are s * scale (no correction, not renormalised). chosen / weight: [n_tokens, top]. */
 int b200_moe_route(const void* h, int h_dtype, const float* w_router, const float* correction, int n_tokens, int width,
                    int n_out, int top, float scale, int* chosen, float* weight, void* stream);
+/* Router that chooses on its logits: z = h W_r^T + bias (fp32 accumulate; bias may be NULL); the `top` largest z are
+ * chosen (ties: the lower index) and their weights are the softmax over the chosen logits only. */
+int b200_moe_route_logits(const void* h, int h_dtype, const float* w_router, const float* bias, int n_tokens, int width,
+                          int n_out, int top, int* chosen, float* weight, void* stream);
 /* Counting sort of the (token, choice) pairs by expert: group_off [n_experts + 1], src_row [n_tokens * top] (token of
  * each sorted row), dest [n_tokens, top] (sorted row of each pair, -1 for chosen >= n_experts: identity experts own no
  * rows). One launch, no host sync. */
@@ -119,10 +126,31 @@ int b200_glu_act(const float* gu, void* out, int n_rows, int n, int epi, int out
 /* v[i] <- cap * tanh(v[i] / cap) */
 int b200_softcap(float* v, size_t n, float cap, void* stream);
 
+/* Residual update fused with the RMS norm of whatever reads the residual next, one launch per sublayer:
+ *   x[t,:] += s1 * y1[t,:] + s2 * y2[t,:] + sum_k weight[t,k] * expert_out[dest[t,k],:] + bcast[:]
+ *   out[t,:] = x[t,:] / sqrt(mean(x[t,:]^2) + eps) * (w_offset + w[:])        (as out_dtype; skipped when w is NULL)
+ * Every addend may be NULL (fp32 sums in this fixed order). With `rows` the call only norms: out[i,:] from x[rows[i],:],
+ * nothing is added. w_offset 1 is a weight stored around zero, 0 a weight stored around one. */
+typedef struct b200_rmsnorm_residual_args {
+    float* x;
+    const float* y1; float s1;
+    const float* y2; float s2;
+    const float* expert_out; const int* dest; const float* weight; int top;
+    const float* bcast;
+    const int* rows;
+    const float* w; float w_offset, eps;
+    void* out; int out_dtype;
+    int n_rows, width;
+} b200_rmsnorm_residual_args;
+int b200_rmsnorm_residual(const b200_rmsnorm_residual_args* a, void* stream);
+
 /* Rotary positions: cos_out / sin_out [n_tokens, n_freq] = cos / sin(pos[t] * freq[i]); the angle is formed and reduced in
  * double precision (freq is a device array of doubles, whatever scaling of the frequencies already applied by the
  * caller), so position 10^5 is as exact as position 1. One launch per step and frequency set, shared by all layers. */
 int b200_rope_angles(const int* pos, int n_tokens, const double* freq, int n_freq, float* cos_out, float* sin_out, void* stream);
+/* the same with both tables multiplied by `amplitude` (designs that stretch q and k together with their frequencies) */
+int b200_rope_angles_amp(const int* pos, int n_tokens, const double* freq, int n_freq, double amplitude, float* cos_out,
+                         float* sin_out, void* stream);
 #define B200_ROPE_HALF 0        /* dimension i pairs with i + dims/2  */
 #define B200_ROPE_INTERLEAVED 1 /* dimension 2i pairs with 2i + 1      */
 
@@ -149,6 +177,9 @@ typedef struct b200_qk_prepare_args {
     int n_tokens, heads, kv_heads, dim, dtype;
     int update_state_inline;   /* 1 (only when EVERY sequence brings exactly one token): the launch also files the token's
                                   inputs in conv_state, and b200_conv_state_update is not needed */
+    /* projected values: v_heads > 0 stores proj[t, v_off + g * vdim + :] unchanged (no convolution, norm or rotation) at the
+       token's row of v_pool [n_pages*page_rows, v_heads, vdim]; not together with v_from_conv */
+    int v_heads, vdim; long long v_off;
 } b200_qk_prepare_args;
 int b200_qk_prepare(const b200_qk_prepare_args* a, void* stream);
 /* The last taps-1 inputs of every sequence of the step go to their ring places (end[t] = the sequence's length after
@@ -173,6 +204,13 @@ typedef struct b200_paged_attention_args {
     int dtype, longest_entry;
     int longest_context;                       /* most rows any token sees (0 = unknown)                          */
     void* workspace; size_t workspace_bytes;   /* shares of split contexts (may be NULL: no splitting)            */
+    /* chunk > 0: position p only sees the keys of its own block of positions, j >= floor(p / chunk) * chunk (blocks are
+       counted from position 0 of the sequence).
+       maps > 1: every query head holds `maps` score maps over the same values: q [n_tokens, heads, maps, dim], k_pool
+       [rows, kv_heads, maps, dim], v_pool [rows, kv_heads, vdim], out [n_tokens, heads, maps, vdim] (map m of head h scores
+       against map m of its key head and weights that head's values). 0 or 1: one map.
+       out_f32 != 0: out is fp32 whatever `dtype` (a caller that combines maps or gates in fp32). */
+    int chunk, maps, out_f32;
 } b200_paged_attention_args;
 size_t b200_paged_attention_workspace_bytes(int n_tokens, int heads, int vdim);
 int b200_paged_attention(const b200_paged_attention_args* a, void* stream);
@@ -199,6 +237,48 @@ int b200_retention(const b200_retention_args* a, void* stream);
  * dimension ld_gate) */
 int b200_unit_rms_gate(const float* o, const float* gate, long long ld_gate, void* out, int n_tokens, int heads, int vdim,
                        float eps, int out_dtype, void* stream);
+/* Differential combination of two attention maps: o = a[t,h,0,:] - lambda * a[t,h,1,:]; out[t,h,:] = o / sqrt(mean(o^2) + eps)
+ * * out_scale, as out_dtype. a fp32 [n_tokens, heads, 2, vdim]. */
+int b200_diff_combine(const float* a, float lambda, float eps, float out_scale, void* out, int n_tokens, int heads, int vdim,
+                      int out_dtype, void* stream);
+/* out[t, c] = o[t, c] * sigmoid(gate[t, c]) as out_dtype; o fp32 [n_tokens, n], gate fp32 with leading dimension ld_gate */
+int b200_sigmoid_gate(const float* o, const float* gate, long long ld_gate, void* out, int n_tokens, int n, int out_dtype,
+                      void* stream);
+
+/* Selective scan (a recurrence with input-dependent step sizes and a diagonal transition per channel), in three pieces.
+ *
+ * b200_conv_act: y[t, c] = silu(bias[c] + sum_j w[c, j] u[(t) - taps + 1 + j, c]) over the channels' own history (zeros
+ * before position 0; inputs older than this step come from conv_state, a ring as in b200_qk_prepare, written afterwards by
+ * b200_conv_state_update). u fp32 [n_tokens, ld_u]; out32 fp32 [n_tokens, channels] and out (out_dtype, the operand of the
+ * next projection) may each be NULL.
+ *
+ * b200_selective_scan: per entry (a run of consecutive tokens of one sequence), channel c and state n, with
+ * dt = softplus(dt_raw[t, c] + dt_bias[c]):
+ *   S[c, n] <- exp(dt * A[c, n]) * S[c, n] + dt * x[t, c] * B[t, n];   y = sum_n S[c, n] * C[t, n] + D[c] * x[t, c]
+ *   out[t, c] = y * silu(z[t, c])        (as out_dtype)
+ * A fp32 [channels, n_state] (already negative), S fp32 [n_slots, channels, n_state], starting from zero when the entry
+ * starts at position 0 and left in place for the next step. x, dt_raw fp32 [n_tokens, channels]; B, C fp32 rows of
+ * leading dimension ld_bc; z fp32 with leading dimension ld_z. All arithmetic fp32. */
+typedef struct b200_conv_act_args {
+    const float* u; long long ld_u; const float* w; const float* bias; int taps; const float* conv_state;
+    float* out32; void* out; int out_dtype;
+    const int* slot; const int* pos; const int* start;
+    int n_tokens, channels;
+    int update_state_inline;   /* as in b200_qk_prepare_args */
+} b200_conv_act_args;
+int b200_conv_act(const b200_conv_act_args* a, void* stream);
+typedef struct b200_selective_scan_args {
+    const float* x; const float* dt_raw; const float* dt_bias;
+    const float* B; const float* C; long long ld_bc;
+    const float* z; long long ld_z;
+    const float* A; const float* D;
+    float* state; void* out; int out_dtype;
+    const int* ent_row; const int* ent_len; const int* slot; const int* pos;
+    int n_entries, n_tokens, channels, n_state, longest_entry;
+    void* workspace; size_t workspace_bytes;   /* chunk summaries of long entries (b200_selective_scan_workspace_bytes) */
+} b200_selective_scan_args;
+size_t b200_selective_scan_workspace_bytes(int n_tokens, int n_entries, int channels, int n_state);
+int b200_selective_scan(const b200_selective_scan_args* a, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * models

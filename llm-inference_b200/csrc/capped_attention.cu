@@ -1,7 +1,9 @@
 // b200_paged_attention: causal attention over paged per-head keys and values with grouped query heads, a tanh cap on
 // the scores and a constant added to the softmax denominator (a sink of score 0 that owns no value). Prompt portions,
 // single decoded tokens and mixed batches run through the same launch: every token carries its sequence slot and
-// position, and only sees its own sequence's pages.
+// position, and only sees its own sequence's pages. Two more masks and layouts are arguments: a block mask (a position
+// only sees the keys of its own block of `chunk` positions) and several score maps per head over shared values (`maps`:
+// query unit (h, m) scores against key unit (h / group, m) and weights the values of key head h / group).
 //
 //   paged_attn_row_kernel   one CTA per (token, query head), fp32 arithmetic on caches of either dtype: each warp
 //                           takes blocks of 32 keys (a lane scores one key; the weighted value sum runs with a lane per
@@ -27,7 +29,15 @@ struct PA {
     int n_tokens, heads, kv_heads, dim, vdim;
     float scale, softcap, denom_bias;
     int splits; float* part;   // row kernel: shares of a context split over gridDim.z CTAs, [token, head, split, 2 + vdim]
+    int chunk, maps, out_f32;
 };
+// first key that position p sees
+__device__ __forceinline__ int pa_first_key(const PA& a, int p) { return a.chunk > 0 ? (p / a.chunk) * a.chunk : 0; }
+template <typename T>
+__device__ __forceinline__ void pa_store(const PA& a, size_t idx, float v) {
+    if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = v;
+    else reinterpret_cast<T*>(a.out)[idx] = DT<T>::from_f(v);
+}
 
 constexpr int kRowWarps = 4;
 constexpr int kMaxSplits = 16;
@@ -66,10 +76,12 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     float* qs = sm;                                   // [dim]
     float* om = sm + a.dim;                           // [kRowWarps][vdim]
     __shared__ float ms[kRowWarps], ls[kRowWarps];
+    // h counts query units (head, map); ku is the key unit it scores against, g the key head whose values it weights
     const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int g = h / (a.heads / a.kv_heads), p = a.pos[t];
+    const int g = (h / a.maps) / (a.heads / a.kv_heads), ku = g * a.maps + h % a.maps, p = a.pos[t];
+    const int k_units = a.kv_heads * a.maps, q_units = a.heads * a.maps;
     const int* plist = a.pages + (size_t)a.slot[t] * a.max_pages;
-    const T* q = reinterpret_cast<const T*>(a.q) + ((size_t)t * a.heads + h) * a.dim;
+    const T* q = reinterpret_cast<const T*>(a.q) + ((size_t)t * q_units + h) * a.dim;
     for (int i = threadIdx.x; i < a.dim; i += blockDim.x) qs[i] = DT<T>::to_f(q[i]);
     __syncthreads();
     const T* K = reinterpret_cast<const T*>(a.k_pool);
@@ -78,17 +90,18 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
 #pragma unroll
     for (int c = 0; c < kMaxVPerLane; ++c) o[c] = 0.f;
     // this CTA's share of the keys: whole blocks of 32, the sink with the first share
-    const int per = ((p + a.splits) / a.splits + 31) & ~31;
-    const int j_begin = blockIdx.z * per, j_end = min(p + 1, j_begin + per);
+    const int j_lo = pa_first_key(a, p);
+    const int per = ((p - j_lo + a.splits) / a.splits + 31) & ~31;
+    const int j_begin = j_lo + blockIdx.z * per, j_end = min(p + 1, j_begin + per);
     if (warp == 0 && blockIdx.z == 0 && a.denom_bias > 0.f) { m = 0.f; l = a.denom_bias; }
     for (int j0 = j_begin + warp * 32; j0 < j_end; j0 += kRowWarps * 32) {
         const int j = j0 + lane;
         const bool ok = j < j_end;
-        size_t row = 0;
+        size_t row = 0;   // the key's row in the page pool
         float s = -INFINITY;
         if (ok) {
-            row = ((size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows) * a.kv_heads + g;
-            s = dot_row<T>(qs, K + row * a.dim, a.dim) * a.scale;
+            row = (size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows;
+            s = dot_row<T>(qs, K + (row * k_units + ku) * a.dim, a.dim) * a.scale;
             if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
         }
         float bm = s;
@@ -108,7 +121,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
         for (int kk = 0; kk < n; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, pj, kk);
             const size_t r = __shfl_sync(0xffffffffu, (unsigned long long)row, kk);
-            const T* vr = V + r * a.vdim;
+            const T* vr = V + (r * a.kv_heads + g) * a.vdim;
 #pragma unroll
             for (int c = 0; c < kMaxVPerLane; ++c)
                 if (lane + 32 * c < a.vdim) o[c] = fmaf(pk, DT<T>::to_f(vr[lane + 32 * c]), o[c]);
@@ -124,7 +137,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     float L = 0.f;
     for (int w = 0; w < kRowWarps; ++w) L += M == -INFINITY ? 0.f : ls[w] * expf(ms[w] - M);
     if (a.splits > 1) {   // an unnormalised share: (m, l, o); an empty share is (-inf, 0, 0)
-        float* pr = a.part + (((size_t)t * a.heads + h) * a.splits + blockIdx.z) * (a.vdim + 2);
+        float* pr = a.part + (((size_t)t * q_units + h) * a.splits + blockIdx.z) * (a.vdim + 2);
         if (threadIdx.x == 0) { pr[0] = M; pr[1] = L; }
         for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
             float v = 0.f;
@@ -133,11 +146,11 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
         }
         return;
     }
-    T* dst = reinterpret_cast<T*>(a.out) + ((size_t)t * a.heads + h) * a.vdim;
+    const size_t dst = ((size_t)t * q_units + h) * a.vdim;
     for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
         float v = 0.f;
         for (int w = 0; w < kRowWarps; ++w) v += om[w * a.vdim + c] * expf(ms[w] - M);
-        dst[c] = DT<T>::from_f(v / L);
+        pa_store<T>(a, dst + c, v / L);
     }
 }
 
@@ -161,11 +174,12 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
     float* om = sc + kRowWarps * R * 32;                   // [warps][R][vdim]
     __shared__ float ms[kRowWarps][R], ls[kRowWarps][R];
     __shared__ unsigned long long rows[kRowWarps][32];
-    const int t = blockIdx.x, g = blockIdx.y, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int p = a.pos[t], dim = a.dim, vdim = a.vdim;
+    // blockIdx.y counts key units (key head g, map mp); query head g * R + r holds its map mp at unit (g * R + r) * maps + mp
+    const int t = blockIdx.x, ku = blockIdx.y, g = ku / a.maps, mp = ku % a.maps, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int p = a.pos[t], dim = a.dim, vdim = a.vdim, k_units = a.kv_heads * a.maps, q_units = a.heads * a.maps;
     const int* plist = a.pages + (size_t)a.slot[t] * a.max_pages;
-    const T* q = reinterpret_cast<const T*>(a.q) + ((size_t)t * a.heads + g * R) * dim;
-    for (int i = threadIdx.x; i < R * dim; i += blockDim.x) qs[i] = DT<T>::to_f(q[i]);
+    const T* q = reinterpret_cast<const T*>(a.q) + (size_t)t * q_units * dim;
+    for (int i = threadIdx.x; i < R * dim; i += blockDim.x) qs[i] = DT<T>::to_f(q[(size_t)((g * R + i / dim) * a.maps + mp) * dim + i % dim]);
     __syncthreads();
     const T* K = reinterpret_cast<const T*>(a.k_pool);
     const T* V = reinterpret_cast<const T*>(a.v_pool);
@@ -178,8 +192,9 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[r][c][0] = o[r][c][1] = 0.f;
     }
-    const int per = ((p + a.splits) / a.splits + 31) & ~31;
-    const int j_begin = blockIdx.z * per, j_end = min(p + 1, j_begin + per);
+    const int j_lo = pa_first_key(a, p);
+    const int per = ((p - j_lo + a.splits) / a.splits + 31) & ~31;
+    const int j_begin = j_lo + blockIdx.z * per, j_end = min(p + 1, j_begin + per);
     float* scw = sc + warp * R * 32;
     const int l8 = lane & 7;
     for (int j0 = j_begin + warp * 32; j0 < j_end; j0 += kRowWarps * 32) {
@@ -191,8 +206,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
             for (int r = 0; r < R; ++r) acc[r] = 0.f;
             size_t row = 0;
             if (j < j_end) {
-                row = ((size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows) * a.kv_heads + g;
-                const T* kr = K + row * dim;
+                row = (size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows;
+                const T* kr = K + (row * k_units + ku) * dim;
                 for (int i = l8 * 8; i < dim; i += 64) {
                     float f[8];
                     if constexpr (sizeof(T) == 2) {   // eight bfloat16 in one 16-byte load
@@ -256,7 +271,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
         const int n = min(32, j_end - j0);
 #pragma unroll 4
         for (int kk = 0; kk < n; ++kk) {   // weighted values, a lane per pair of columns
-            const T* vr = V + rows[warp][kk] * vdim;
+            const T* vr = V + (rows[warp][kk] * a.kv_heads + g) * vdim;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int col = 2 * lane + 64 * c;
@@ -284,19 +299,19 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
     }
     __syncthreads();
     for (int r = 0; r < R; ++r) {
-        const int h = g * R + r;
+        const int h = (g * R + r) * a.maps + mp;   // query unit
         float M = ms[0][r];
         for (int w = 1; w < kRowWarps; ++w) M = fmaxf(M, ms[w][r]);
         float L = 0.f;
         for (int w = 0; w < kRowWarps; ++w) L += M == -INFINITY ? 0.f : ls[w][r] * expf(ms[w][r] - M);
-        float* pr = a.splits > 1 ? a.part + (((size_t)t * a.heads + h) * a.splits + blockIdx.z) * (vdim + 2) : nullptr;
+        float* pr = a.splits > 1 ? a.part + (((size_t)t * q_units + h) * a.splits + blockIdx.z) * (vdim + 2) : nullptr;
         if (pr && threadIdx.x == 0) { pr[0] = M; pr[1] = L; }
-        T* dst = reinterpret_cast<T*>(a.out) + ((size_t)t * a.heads + h) * vdim;
+        const size_t dst = ((size_t)t * q_units + h) * vdim;
         for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
             float v = 0.f;
             for (int w = 0; w < kRowWarps; ++w) v += M == -INFINITY ? 0.f : om[(w * R + r) * vdim + c] * expf(ms[w][r] - M);
             if (pr) pr[2 + c] = v;
-            else dst[c] = DT<T>::from_f(v / L);
+            else pa_store<T>(a, dst + c, v / L);
         }
     }
 }
@@ -377,7 +392,9 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
     int* row_pos = reinterpret_cast<int*>(Vs + 2 * kTileN * RS);   // [64], -1: no such row
     int* row_slot = row_pos + kTileM;
     // the last rows of a prompt see the most keys: those tiles are scheduled first, the short ones fill the tail
-    const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTileM, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+    const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTileM, h = blockIdx.y;   // h: query unit (head, map)
+    const int g = (h / a.maps) / (a.heads / a.kv_heads), ku = g * a.maps + h % a.maps;
+    const int k_units = a.kv_heads * a.maps, q_units = a.heads * a.maps;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gid = lane >> 2, tig = lane & 3;
     const int rows = min(kTileM, a.n_tokens - t0);
     for (int r = threadIdx.x; r < kTileM; r += blockDim.x) {
@@ -388,7 +405,7 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
     for (int i = threadIdx.x; i < kTileM * CH; i += blockDim.x) {
         const int r = i / CH, c = i % CH;
         Pack16 v{{0u, 0u, 0u, 0u}};
-        if (r < rows) v = ld16(Q + ((size_t)(t0 + r) * a.heads + h) * D + c * 8);
+        if (r < rows) v = ld16(Q + ((size_t)(t0 + r) * q_units + h) * D + c * 8);
         st16(Qs + r * RS + c * 8, v);
     }
     __syncthreads();
@@ -411,35 +428,38 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
         int seg_end = seg + 1;
         while (seg_end < rows && row_slot[seg_end] == b) ++seg_end;
         const int n_keys = row_pos[seg_end - 1] + 1;            // positions grow along an entry
+        const int first_key = pa_first_key(a, row_pos[seg]);    // with a block mask the first row's block starts the walk
         const int* plist = a.pages + (size_t)b * a.max_pages;
-        // this thread's two rows in this segment, and the last key any row of the warp sees
+        // this thread's two rows in this segment (last and first key each sees), and the keys any row of the warp sees
         const int p_lo = (r_lo >= seg && r_lo < seg_end) ? row_pos[r_lo] : -1;
         const int p_hi = (r_hi >= seg && r_hi < seg_end) ? row_pos[r_hi] : -1;
+        const int f_lo = p_lo >= 0 ? pa_first_key(a, p_lo) : 0, f_hi = p_hi >= 0 ? pa_first_key(a, p_hi) : 0;
         const int w_first = max(seg, warp * 16), w_last = min(seg_end, warp * 16 + 16) - 1;
         const int warp_keys = w_last >= w_first ? row_pos[w_last] + 1 : 0;
+        const int warp_first = w_last >= w_first ? pa_first_key(a, row_pos[w_first]) : 0;
         auto load_tile = [&](int k0, int buf) {
             bf* kd = Ks + buf * kTileN * RS;
             bf* vd = Vs + buf * kTileN * RS;
             for (int i = threadIdx.x; i < kTileN * CH; i += blockDim.x) {
                 const int kr = i / CH, c = i % CH, j = k0 + kr;
                 const bool ok = j < n_keys;
-                const size_t row = ok ? ((size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows) * a.kv_heads + g : 0;
+                const size_t row = ok ? (size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows : 0;
                 const uint32_t bytes = ok ? 16u : 0u;                 // beyond the sequence: zeros, nothing is read
                 const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(kd + kr * RS + c * 8);
                 const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(vd + kr * RS + c * 8);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + row * D + c * 8), "r"(bytes) : "memory");
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + row * D + c * 8), "r"(bytes) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + (row * k_units + ku) * D + c * 8), "r"(bytes) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + (row * a.kv_heads + g) * D + c * 8), "r"(bytes) : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
         __syncthreads();   // the buffers of the previous segment are no longer read
-        load_tile(0, 0);
+        load_tile(first_key, 0);
         int buf = 0;
-        for (int k0 = 0; k0 < n_keys; k0 += kTileN, buf ^= 1) {
+        for (int k0 = first_key; k0 < n_keys; k0 += kTileN, buf ^= 1) {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();   // tile k0 has landed for everybody; the other buffer is no longer read
             if (k0 + kTileN < n_keys) load_tile(k0 + kTileN, buf ^ 1);
-            if (k0 >= warp_keys) continue;   // causal: nothing for this warp's rows from here on (it keeps the barriers)
+            if (k0 >= warp_keys || k0 + kTileN <= warp_first) continue;   // nothing for this warp's rows in this tile (it keeps the barriers)
             const bf* Kb = Ks + buf * kTileN * RS;
             const bf* Vb = Vs + buf * kTileN * RS;
             float s[kTileN / 8][4];
@@ -502,7 +522,7 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = k0 + nt * 8 + tig * 2 + (e & 1);
-                    const float v = j <= ((e & 2) ? p_hi : p_lo) ? s[nt][e] : -INFINITY;
+                    const float v = (j <= ((e & 2) ? p_hi : p_lo) && j >= ((e & 2) ? f_hi : f_lo)) ? s[nt][e] : -INFINITY;
                     s[nt][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -551,16 +571,21 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
         }
         seg = seg_end;
     }
-    bf* out = reinterpret_cast<bf*>(a.out);
 #pragma unroll
     for (int hrow = 0; hrow < 2; ++hrow) {
         const int r = hrow ? r_hi : r_lo;
         if (r >= rows) continue;
         const float inv = 1.0f / l_run[hrow];
-        bf* dst = out + ((size_t)(t0 + r) * a.heads + h) * D + tig * 2;
+        const size_t dst = ((size_t)(t0 + r) * q_units + h) * D + tig * 2;
+        if (a.out_f32) {
 #pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt)
-            *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) = __floats2bfloat162_rn(o[nt][hrow * 2] * inv, o[nt][hrow * 2 + 1] * inv);
+            for (int nt = 0; nt < D / 8; ++nt)
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + dst + nt * 8) = make_float2(o[nt][hrow * 2] * inv, o[nt][hrow * 2 + 1] * inv);
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt)
+                *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf*>(a.out) + dst + nt * 8) = __floats2bfloat162_rn(o[nt][hrow * 2] * inv, o[nt][hrow * 2 + 1] * inv);
+        }
     }
 }
 
@@ -571,7 +596,7 @@ static int launch_tile(const PA& a, cudaStream_t s) {
     static unsigned long long done = 0;
     const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D>, smem, done);
     if (e != cudaSuccess) return (int)e;
-    paged_attn_tile_kernel<D><<<dim3((a.n_tokens + kTileM - 1) / kTileM, a.heads), 128, smem, s>>>(a);
+    paged_attn_tile_kernel<D><<<dim3((a.n_tokens + kTileM - 1) / kTileM, a.heads * a.maps), 128, smem, s>>>(a);
     return (int)cudaGetLastError();
 }
 
@@ -586,12 +611,14 @@ extern "C" size_t b200_paged_attention_workspace_bytes(int n_tokens, int heads, 
 
 extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* stream) {
     if (!p || !p->q || !p->out || !p->k_pool || !p->v_pool || !p->pages || !p->slot || !p->pos || p->n_tokens < 0 || p->heads < 1 ||
-        p->kv_heads < 1 || p->heads % p->kv_heads || p->dim < 1 || p->vdim < 1 || p->page_rows < 1 || p->denom_bias < 0.f)
+        p->kv_heads < 1 || p->heads % p->kv_heads || p->dim < 1 || p->vdim < 1 || p->page_rows < 1 || p->denom_bias < 0.f ||
+        p->chunk < 0 || p->maps < 0)
         return B200_EINVAL;
+    const int maps = p->maps > 0 ? p->maps : 1, units = p->heads * maps;
     if (p->vdim > 32 * kMaxVPerLane) return B200_EUNSUPPORTED;
     if (p->n_tokens == 0) return B200_OK;
     PA a{p->q, p->out, p->k_pool, p->v_pool, p->pages, p->max_pages, p->page_rows, p->slot, p->pos, p->n_tokens, p->heads,
-         p->kv_heads, p->dim, p->vdim, p->scale, p->softcap, p->denom_bias, 1, nullptr};
+         p->kv_heads, p->dim, p->vdim, p->scale, p->softcap, p->denom_bias, 1, nullptr, p->chunk, maps, p->out_f32};
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = ((size_t)p->dim + (size_t)kRowWarps * p->vdim) * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
@@ -608,20 +635,21 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
     const bool group = p->longest_entry == 1 && (R == 1 || R == 2 || R == 4 || R == 8) && p->dim % 8 == 0 && p->vdim % 2 == 0 &&
                        al16(p->k_pool) && al16(p->v_pool) && !(env && env[0] == '1') &&
                        ((size_t)R * p->dim + (size_t)kRowWarps * R * (32 + p->vdim)) * sizeof(float) <= 48 * 1024;
-    const long long ctas = (long long)p->n_tokens * (group ? p->kv_heads : p->heads);
+    const long long ctas = (long long)p->n_tokens * (group ? p->kv_heads * maps : units);
     // few rows with long contexts (decode batches): split every context over several CTAs and merge the shares
-    if (p->longest_context > 256 && p->workspace && (long long)p->n_tokens * p->heads < 2 * sm_count()) {
+    const int longest_seen = p->chunk > 0 ? std::min(p->longest_context, p->chunk) : p->longest_context;
+    if (longest_seen > 256 && p->workspace && (long long)p->n_tokens * units < 2 * sm_count()) {
         int splits = (int)((4ll * sm_count() + ctas - 1) / ctas);
-        splits = std::min(std::min(splits, kMaxSplits), (p->longest_context + 127) / 128);
-        if (splits > 1 && p->workspace_bytes >= (size_t)p->n_tokens * p->heads * splits * (p->vdim + 2) * sizeof(float)) {
+        splits = std::min(std::min(splits, kMaxSplits), (longest_seen + 127) / 128);
+        if (splits > 1 && p->workspace_bytes >= (size_t)p->n_tokens * units * splits * (p->vdim + 2) * sizeof(float)) {
             a.splits = splits;
             a.part = reinterpret_cast<float*>(p->workspace);
         }
     }
-    const dim3 grid3(p->n_tokens, p->heads, a.splits);
+    const dim3 grid3(p->n_tokens, units, a.splits);
     bool done = false;
     if (group) {
-        const dim3 gridg(p->n_tokens, p->kv_heads, a.splits);
+        const dim3 gridg(p->n_tokens, p->kv_heads * maps, a.splits);
         done = p->dtype == B200_BF16 ? launch_group<__nv_bfloat16>(a, gridg, s) : p->dtype == B200_F32 ? launch_group<float>(a, gridg, s) : false;
     }
     if (done) {
@@ -630,8 +658,8 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
     else return B200_EINVAL;
     count_launch();
     if (a.splits > 1) {
-        if (p->dtype == B200_BF16) paged_attn_combine_kernel<__nv_bfloat16><<<p->n_tokens * p->heads, 128, 0, s>>>(a.part, (__nv_bfloat16*)p->out, a.splits, p->vdim);
-        else paged_attn_combine_kernel<float><<<p->n_tokens * p->heads, 128, 0, s>>>(a.part, (float*)p->out, a.splits, p->vdim);
+        if (p->dtype == B200_BF16 && !p->out_f32) paged_attn_combine_kernel<__nv_bfloat16><<<p->n_tokens * units, 128, 0, s>>>(a.part, (__nv_bfloat16*)p->out, a.splits, p->vdim);
+        else paged_attn_combine_kernel<float><<<p->n_tokens * units, 128, 0, s>>>(a.part, (float*)p->out, a.splits, p->vdim);
         count_launch();
     }
     return (int)cudaGetLastError();

@@ -35,6 +35,7 @@ __device__ __forceinline__ void gg_store(const GG& g, TC* C, long long row, int 
     if (g.epi == B200_GG_SIGMOID_MUL) v *= 1.f / (1.f + expf(-g.aux[aux_off + row * g.ld_aux + col]));
     else if (g.epi == B200_GG_GLU) v = v / (1.f + expf(-v)) * v2;
     else if (g.epi == B200_GG_GLU_GELU) v = gelu_tanh_f(v) * v2;
+    else if (g.epi == B200_GG_RELU2) { v = fmaxf(v, 0.f); v *= v; }
     C[row * g.ldc + col] = DT<TC>::from_f(v);
 }
 
@@ -359,7 +360,7 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
 }
 
 int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, int glu, void* workspace,
-                    size_t workspace_bytes, cudaStream_t s);   // gemm_tcgen05.cu (glu: 0 none, 1 silu, 2 tanh-gelu)
+                    size_t workspace_bytes, cudaStream_t s);   // gemm_tcgen05.cu (glu: 0 none, 1 silu, 2 tanh-gelu, 3 no GLU but relu squared)
 size_t gemm_tcgen05_ex_workspace_bytes(int M, int N, int K);
 
 static bool mma_enabled() {
@@ -415,10 +416,10 @@ extern "C" size_t b200_linear_ex_workspace_bytes(int n_tokens, int N, int K) {
 
 extern "C" int b200_linear_ex(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
                               void* workspace, size_t workspace_bytes, void* stream) {
-    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 || (epi != B200_GG_NONE && epi != B200_GG_GLU && epi != B200_GG_GLU_GELU)) return B200_EINVAL;
+    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 || (epi != B200_GG_NONE && epi != B200_GG_GLU && epi != B200_GG_GLU_GELU && epi != B200_GG_RELU2)) return B200_EINVAL;
     if (n_tokens == 0) return B200_OK;
     if (in_dtype == B200_BF16 && (out_dtype == B200_BF16 || out_dtype == B200_F32)) {
-        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, epi == B200_GG_GLU ? 1 : epi == B200_GG_GLU_GELU ? 2 : 0, workspace,
+        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, epi == B200_GG_GLU ? 1 : epi == B200_GG_GLU_GELU ? 2 : epi == B200_GG_RELU2 ? 3 : 0, workspace,
                                        workspace_bytes, (cudaStream_t)stream);
         if (rc != B200_EUNSUPPORTED) return rc;
     }

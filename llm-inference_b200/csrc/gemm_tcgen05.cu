@@ -45,7 +45,12 @@ struct GemmParams {
     int in_bf16;        // operands are bfloat16 instead of fp16 (same tiles, other instruction descriptor)
     int out_kind;       // element type of C: 0 fp16 (rounding points of the reference sequence), 1 bfloat16, 2 fp32
     int glu_act;        // GLU epilogue: 0 silu, 1 gelu in its tanh form (out_kind 1 / 2 only)
+    int unary;          // plain epilogue: 0 none, 1 the square of relu on every output (after the split-K sum, if any)
 };
+__device__ __forceinline__ float gemm_unary(float v, int unary) {
+    if (unary == 1) { v = fmaxf(v, 0.f); v *= v; }
+    return v;
+}
 
 template <int BN>
 struct GemmSmem {
@@ -247,6 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 for (int e = 0; e < 8; ++e) {
                                     f[e] = __uint_as_float(v[q * 8 + e]);
                                     if (bias) f[e] += __half2float(bias[col0 + q * 8 + e]);
+                                    f[e] = gemm_unary(f[e], p.unary);
                                 }
                                 store8(C, dst + q * 8, f, ok);
                             }
@@ -258,7 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (col0 + j >= p.rows_b) continue;
                                 float f = __uint_as_float(v[j]);
                                 if (bias) f += __half2float(bias[col0 + j]);
-                                store1(C, dst + j, f, ok);
+                                store1(C, dst + j, gemm_unary(f, p.unary), ok);
                             }
                         }
                     }
@@ -274,7 +280,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (p.partial)
                                     p.partial[((size_t)sp * p.tokens + tok) * p.ldc + row] = f;
                                 else
-                                    store1(C, (size_t)tok * p.ldc + row, f + bv, ok);
+                                    store1(C, (size_t)tok * p.ldc + row, gemm_unary(f + bv, p.unary), ok);
                             }
                         }
                     }
@@ -298,7 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // split-K reduction: y[tok, n] = half(sum_s partial[s, tok, n] + bias[n])
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, const __half* __restrict__ bias, void* __restrict__ y,
-                     int splits, size_t elems, int ldc, int out_kind) {
+                     int splits, size_t elems, int ldc, int out_kind, int unary) {
     pdl_wait();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= elems) return;
@@ -313,6 +319,8 @@ splitk_reduce_kernel(const float* __restrict__ partial, const __half* __restrict
         acc.z += __half2float(bias[n + 2]); acc.w += __half2float(bias[n + 3]);
     }
     pdl_launch_dependents();
+    acc.x = gemm_unary(acc.x, unary); acc.y = gemm_unary(acc.y, unary);
+    acc.z = gemm_unary(acc.z, unary); acc.w = gemm_unary(acc.w, unary);
     if (out_kind == 0) {
         __half2* out = reinterpret_cast<__half2*>(reinterpret_cast<__half*>(y) + i);
         out[0] = __floats2half2_rn(acc.x, acc.y);
@@ -470,7 +478,7 @@ int gemm_tcgen05_f16(const void* x, const void* W, const void* bias, void* y, in
         if (rc != 0 || p.splits == 1) return rc;
         const size_t elems = (size_t)M * N;
         cudaError_t e = launch_k(splitk_reduce_kernel, dim3((unsigned)((elems / 4 + 255) / 256)), dim3(256), 0, s, true,
-                                 (const float*)p.partial, (const __half*)bias, y, p.splits, elems, N, 0);
+                                 (const float*)p.partial, (const __half*)bias, y, p.splits, elems, N, 0, 0);
         count_launch();
         return (int)e;
     }
@@ -494,7 +502,8 @@ int gemm_tcgen05_f16(const void* x, const void* W, const void* bias, void* y, in
 }
 
 // The same single-CTA kernel for the model families of b200_serve.h: operands fp16 or bfloat16, output fp16 / bfloat16 /
-// fp32 (out_kind as GemmParams), optionally with the GLU epilogue (W = [2 N, K], gate rows then up rows, N % 128 == 0).
+// fp32 (out_kind as GemmParams), optionally with the GLU epilogue (glu 1 silu, 2 tanh-gelu: W = [2 N, K], gate rows then up
+// rows, N % 128 == 0) or with the square of relu on every output (glu 3: not a GLU, W = [N, K]).
 // Up to 256 token rows the weights stream through the M axis (swapped, split-K); above, tokens are the M axis.
 int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, int glu, void* workspace,
                     size_t workspace_bytes, cudaStream_t s) {
@@ -507,6 +516,8 @@ int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, 
     p.C = y; p.bias = nullptr; p.K = K; p.ldc = N; p.tokens = M;
     p.k_blocks = (K + kBK - 1) / kBK;
     p.in_bf16 = in_bf16; p.out_kind = out_kind; p.glu_act = glu == 2;
+    p.unary = glu == 3 ? 1 : 0;
+    if (glu == 3) glu = 0;
     CUtensorMap ma, mb;
     if (glu) {
         if (N < 128 || (N & 127)) return B200_EUNSUPPORTED;
@@ -539,7 +550,7 @@ int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, 
         if (rc != 0 || p.splits == 1) return rc;
         const size_t elems = (size_t)M * N;
         cudaError_t e = launch_k(splitk_reduce_kernel, dim3((unsigned)((elems / 4 + 255) / 256)), dim3(256), 0, s, true,
-                                 (const float*)p.partial, (const __half*)nullptr, y, p.splits, elems, N, out_kind);
+                                 (const float*)p.partial, (const __half*)nullptr, y, p.splits, elems, N, out_kind, p.unary);
         count_launch();
         return (int)e;
     }

@@ -1,5 +1,5 @@
-// Mixture-of-experts plumbing around b200_gemm_grouped: router (softmax over all outputs, corrected choice, identity
-// experts), counting sort of the (token, choice) pairs by expert, and the fp32 residual update that gathers every
+// Mixture-of-experts plumbing around b200_gemm_grouped: routers (softmax over all outputs with a corrected choice and
+// identity experts; or a choice on the biased logits with a softmax over the chosen ones), counting sort of the (token, choice) pairs by expert, and the fp32 residual update that gathers every
 // token's expert rows back in a fixed order (no atomics: a token's sum does not depend on the batch around it).
 #include "b200_serve.h"
 #include "common.cuh"
@@ -11,7 +11,8 @@ namespace b200 {
 // thread 0 the softmax and the choice
 template <typename T>
 __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
-                                                        const float* __restrict__ corr, int width, int n_out, int top,
+                                                        const float* __restrict__ corr, const float* __restrict__ bias,
+                                                        int on_logits, int width, int n_out, int top,
                                                         float scale, int* __restrict__ chosen, float* __restrict__ weight) {
     extern __shared__ float z[];   // z[n_out] | pick[n_out] | x[width]
     float* pick = z + n_out;
@@ -43,10 +44,24 @@ __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h,
         float d = (d0 + d1) + (d2 + d3);
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
-        if (lane == 0) z[o] = d;
+        if (lane == 0) z[o] = d + (bias ? bias[o] : 0.f);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && on_logits) {   // the `top` largest logits, then a softmax over those alone
+        float m = -INFINITY, den = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = 0;
+            float bv = -INFINITY;
+            for (int o = 0; o < n_out; ++o)
+                if (z[o] > bv) { bv = z[o]; best = o; }   // ties: lower index
+            z[best] = -INFINITY;
+            if (k == 0) m = bv;                            // the first pick is the largest
+            chosen[(size_t)t * top + k] = best;
+            pick[k] = expf(bv - m);
+            den += pick[k];
+        }
+        for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] = pick[k] / den;
+    } else if (threadIdx.x == 0) {
         float m = -INFINITY, den = 0.f;
         for (int o = 0; o < n_out; ++o) m = fmaxf(m, z[o]);
         for (int o = 0; o < n_out; ++o) { z[o] = expf(z[o] - m); den += z[o]; }
@@ -136,11 +151,30 @@ extern "C" int b200_moe_route(const void* h, int h_dtype, const float* w_router,
     const size_t smem = ((size_t)2 * n_out + width) * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
     if (h_dtype == B200_BF16)
-        moe_route_kernel<__nv_bfloat16><<<n_tokens, 512, smem, s>>>((const __nv_bfloat16*)h, w_router, correction, width, n_out, top,
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, 512, smem, s>>>((const __nv_bfloat16*)h, w_router, correction, nullptr, 0, width, n_out, top,
                                                                    scale, chosen, weight);
     else if (h_dtype == B200_F32)
-        moe_route_kernel<float><<<n_tokens, 512, smem, s>>>((const float*)h, w_router, correction, width, n_out, top, scale, chosen,
+        moe_route_kernel<float><<<n_tokens, 512, smem, s>>>((const float*)h, w_router, correction, nullptr, 0, width, n_out, top, scale, chosen,
                                                            weight);
+    else
+        return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_moe_route_logits(const void* h, int h_dtype, const float* w_router, const float* bias, int n_tokens, int width,
+                                     int n_out, int top, int* chosen, float* weight, void* stream) {
+    if (!h || !w_router || !chosen || !weight || n_tokens < 0 || width < 1 || n_out < 1 || top < 1 || top > n_out) return B200_EINVAL;
+    if (n_out > 4096) return B200_EUNSUPPORTED;
+    if (n_tokens == 0) return B200_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = ((size_t)2 * n_out + width) * sizeof(float);
+    if (smem > 48 * 1024) return B200_EUNSUPPORTED;
+    if (h_dtype == B200_BF16)
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, 512, smem, s>>>((const __nv_bfloat16*)h, w_router, nullptr, bias, 1, width, n_out, top, 1.f,
+                                                                   chosen, weight);
+    else if (h_dtype == B200_F32)
+        moe_route_kernel<float><<<n_tokens, 512, smem, s>>>((const float*)h, w_router, nullptr, bias, 1, width, n_out, top, 1.f, chosen, weight);
     else
         return B200_EINVAL;
     count_launch();

@@ -1,0 +1,97 @@
+// b200_rmsnorm_residual: the fp32 residual update of a pre-norm layer (up to two scaled sublayer outputs, the weighted
+// rows of routed experts, a vector shared by all rows) fused with the RMS norm of whatever reads the residual next, so a
+// sublayer boundary is one launch. One CTA per row; the new row stays in shared memory between the sum of squares and
+// the output. With a row list the kernel only norms the listed rows (the final norm before the vocabulary projection).
+#include "b200_serve.h"
+#include "common.cuh"
+#include "launch_count.h"
+
+namespace b200 {
+
+struct RnArgs {
+    float* x;
+    const float* y1; float s1;
+    const float* y2; float s2;
+    const float* eo; const int* dest; const float* weight; int top;
+    const float* bcast;
+    const int* rows;
+    const float* w; float w_offset, eps;
+    void* out;
+    int width;
+};
+
+constexpr int kRnThreads = 256, kRnMaxTop = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(kRnThreads) rmsnorm_residual_kernel(const RnArgs a) {
+    extern __shared__ float rn_row[];
+    __shared__ float red[kRnThreads / 32];
+    __shared__ int e_dest[kRnMaxTop];
+    __shared__ float e_w[kRnMaxTop];
+    const int i = blockIdx.x, width = a.width;
+    const size_t src = (size_t)(a.rows ? a.rows[i] : i) * width;
+    const bool adds = !a.rows && (a.y1 || a.y2 || a.eo || a.bcast);
+    if (a.eo && threadIdx.x < a.top) {
+        e_dest[threadIdx.x] = a.dest[(size_t)i * a.top + threadIdx.x];
+        e_w[threadIdx.x] = a.weight[(size_t)i * a.top + threadIdx.x];
+    }
+    if (a.eo) __syncthreads();
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += kRnThreads) {
+        float v = a.x[src + c];
+        if (adds) {
+            if (a.y1) v += a.s1 * a.y1[src + c];
+            if (a.y2) v += a.s2 * a.y2[src + c];
+            if (a.eo) {
+                float r = 0.f;
+                for (int k = 0; k < a.top; ++k)
+                    if (e_dest[k] >= 0) r = fmaf(e_w[k], a.eo[(size_t)e_dest[k] * width + c], r);
+                v += r;
+            }
+            if (a.bcast) v += a.bcast[c];
+            a.x[src + c] = v;
+        }
+        rn_row[c] = v;
+        ss += v * v;
+    }
+    if (!a.w) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < kRnThreads / 32; ++k) tot += red[k];   // the same order in every thread
+    const float rinv = 1.0f / sqrtf(tot / (float)width + a.eps);
+    T* out = reinterpret_cast<T*>(a.out) + (size_t)i * width;
+    for (int c = threadIdx.x; c < width; c += kRnThreads) out[c] = DT<T>::from_f(rn_row[c] * rinv * (a.w_offset + a.w[c]));
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_rmsnorm_residual(const b200_rmsnorm_residual_args* p, void* stream) {
+    if (!p || !p->x || p->n_rows < 0 || p->width < 1) return B200_EINVAL;
+    if (p->w && !p->out) return B200_EINVAL;
+    if (p->expert_out && (!p->dest || !p->weight || p->top < 1)) return B200_EINVAL;
+    if (p->expert_out && p->top > kRnMaxTop) return B200_EUNSUPPORTED;
+    if (p->rows && (p->y1 || p->y2 || p->expert_out || p->bcast)) return B200_EINVAL;
+    if (p->n_rows == 0) return B200_OK;
+    const size_t smem = (size_t)p->width * sizeof(float);
+    if (smem > 200 * 1024) return B200_EUNSUPPORTED;
+    RnArgs a{p->x, p->y1, p->s1, p->y2, p->s2, p->expert_out, p->dest, p->weight, p->top, p->bcast, p->rows, p->w, p->w_offset, p->eps,
+             p->out, p->width};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p->out_dtype == B200_BF16 || !p->w) {
+        static unsigned long long done = 0;
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)rmsnorm_residual_kernel<__nv_bfloat16>, 200 * 1024, done);
+        rmsnorm_residual_kernel<__nv_bfloat16><<<p->n_rows, kRnThreads, smem, s>>>(a);
+    } else if (p->out_dtype == B200_F32) {
+        static unsigned long long done = 0;
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)rmsnorm_residual_kernel<float>, 200 * 1024, done);
+        rmsnorm_residual_kernel<float><<<p->n_rows, kRnThreads, smem, s>>>(a);
+    } else
+        return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}

@@ -10,14 +10,14 @@
 namespace b200 {
 
 __global__ void rope_angles_kernel(const int* __restrict__ pos, const double* __restrict__ freq, int n_freq, int total,
-                                   float* __restrict__ cos_out, float* __restrict__ sin_out) {
+                                   double amplitude, float* __restrict__ cos_out, float* __restrict__ sin_out) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const double a = (double)pos[i / n_freq] * freq[i % n_freq];
     double s, c;
     sincos(a, &s, &c);
-    cos_out[i] = (float)c;
-    sin_out[i] = (float)s;
+    cos_out[i] = (float)(amplitude * c);
+    sin_out[i] = (float)(amplitude * s);
 }
 
 struct QkPrep {
@@ -30,6 +30,7 @@ struct QkPrep {
     const int* pages; int max_pages, page_rows;
     const int* slot; const int* pos; const int* start;
     int heads, kv_heads, dim;
+    int v_heads, vdim; long long v_off;
 };
 
 // One warp per (token, head unit): units [0, heads) are query heads, [heads, heads + kv_heads) key heads; a lane owns the
@@ -43,7 +44,15 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
     const int unit = blockIdx.x * kPrepWarps + warp, per_token = a.heads + a.kv_heads;
     if (unit >= n_units) return;
     float* vals = prep_sm + warp * dim;   // the normed head before rotation
-    const int t = unit / per_token, u = unit % per_token;
+    const int t = unit / (per_token + a.v_heads), u = unit % (per_token + a.v_heads);
+    if (u >= per_token) {   // a projected value head: copied to its cache row as it is
+        const int g = u - per_token, pv = a.pos[t];
+        const size_t vrow = ((size_t)a.pages[(size_t)a.slot[t] * a.max_pages + pv / a.page_rows] * a.page_rows + pv % a.page_rows) * a.v_heads + g;
+        const float* src = a.proj + (size_t)t * a.ld_proj + a.v_off + (size_t)g * a.vdim;
+        T* vd = reinterpret_cast<T*>(a.v_pool) + vrow * a.vdim;
+        for (int i = lane; i < a.vdim; i += 32) vd[i] = DT<T>::from_f(src[i]);
+        return;
+    }
     const bool is_k = u >= a.heads;
     const int ch0 = u * dim;          // first channel of this head in [q channels | k channels]
     const int channels = per_token * dim;
@@ -147,14 +156,18 @@ __global__ void conv_state_update_kernel(const float* __restrict__ proj, long lo
 
 using namespace b200;
 
-extern "C" int b200_rope_angles(const int* pos, int n_tokens, const double* freq, int n_freq, float* cos_out, float* sin_out,
-                                void* stream) {
+extern "C" int b200_rope_angles_amp(const int* pos, int n_tokens, const double* freq, int n_freq, double amplitude, float* cos_out,
+                                    float* sin_out, void* stream) {
     if (!pos || !freq || !cos_out || !sin_out || n_tokens < 0 || n_freq < 0) return B200_EINVAL;
     const int total = n_tokens * n_freq;
     if (total == 0) return B200_OK;
-    rope_angles_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, freq, n_freq, total, cos_out, sin_out);
+    rope_angles_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, freq, n_freq, total, amplitude, cos_out, sin_out);
     count_launch();
     return (int)cudaGetLastError();
+}
+extern "C" int b200_rope_angles(const int* pos, int n_tokens, const double* freq, int n_freq, float* cos_out, float* sin_out,
+                                void* stream) {
+    return b200_rope_angles_amp(pos, n_tokens, freq, n_freq, 1.0, cos_out, sin_out, stream);
 }
 
 extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
@@ -163,14 +176,15 @@ extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
         return B200_EINVAL;
     if (p->conv_w && (p->taps < 1 || !p->start || (p->taps > 1 && !p->conv_state))) return B200_EINVAL;
     if (p->v_from_conv && !p->v_pool) return B200_EINVAL;
+    if (p->v_heads < 0 || (p->v_heads > 0 && (!p->v_pool || p->vdim < 1 || p->v_from_conv || p->v_off < 0))) return B200_EINVAL;
     if (p->rot_dims < 0 || (p->rot_dims & 1) || p->rot_dims > p->dim || (p->rot_dims && (!p->cos || !p->sin))) return B200_EINVAL;
     if (p->rot_layout != B200_ROPE_HALF && p->rot_layout != B200_ROPE_INTERLEAVED) return B200_EINVAL;
     if (p->n_tokens == 0) return B200_OK;
     QkPrep a{p->proj, p->ld_proj, p->conv_w, p->taps, p->conv_state, p->q_norm, p->k_norm, p->eps, p->cos, p->sin, p->rot_dims,
              p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->update_state_inline ? const_cast<float*>(p->conv_state) : nullptr, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
-             p->start, p->heads, p->kv_heads, p->dim};
+             p->start, p->heads, p->kv_heads, p->dim, p->v_heads, p->vdim, p->v_off};
     if (a.conv_w && a.taps == 1) a.conv_state = a.proj;   // never read: every input of a one-tap filter is the token's own
-    const long long units = (long long)p->n_tokens * (p->heads + p->kv_heads);
+    const long long units = (long long)p->n_tokens * (p->heads + p->kv_heads + p->v_heads);
     if (units > 0x7fffffffll) return B200_EUNSUPPORTED;
     const unsigned grid = (unsigned)((units + kPrepWarps - 1) / kPrepWarps);
     const size_t smem = (size_t)kPrepWarps * p->dim * sizeof(float);

@@ -8,7 +8,7 @@ import numpy as np
 from . import capi
 
 F32, BF16 = 0, 2
-GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU = 0, 1, 2, 3
+GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU, GG_RELU2 = 0, 1, 2, 3, 4
 ROPE_HALF, ROPE_INTERLEAVED = 0, 1
 _vp, _i, _f, _sz, _ll = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_longlong
 
@@ -28,7 +28,8 @@ class QkPrepareArgs(C.Structure):
                 ("q_norm", _vp), ("k_norm", _vp), ("eps", _f), ("cos", _vp), ("sin", _vp), ("rot_dims", _i), ("rot_layout", _i),
                 ("q_out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("v_from_conv", _i),
                 ("pages", _vp), ("max_pages", _i), ("page_rows", _i), ("slot", _vp), ("pos", _vp), ("start", _vp),
-                ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("dtype", _i), ("update_state_inline", _i)]
+                ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("dtype", _i), ("update_state_inline", _i),
+                ("v_heads", _i), ("vdim", _i), ("v_off", _ll)]
 
 
 class PagedAttentionArgs(C.Structure):
@@ -36,7 +37,31 @@ class PagedAttentionArgs(C.Structure):
     _fields_ = [("q", _vp), ("out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("pages", _vp), ("max_pages", _i), ("page_rows", _i),
                 ("slot", _vp), ("pos", _vp), ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("vdim", _i),
                 ("scale", _f), ("softcap", _f), ("denom_bias", _f), ("dtype", _i), ("longest_entry", _i),
-                ("longest_context", _i), ("workspace", _vp), ("workspace_bytes", _sz)]
+                ("longest_context", _i), ("workspace", _vp), ("workspace_bytes", _sz),
+                ("chunk", _i), ("maps", _i), ("out_f32", _i)]
+
+
+class RmsnormResidualArgs(C.Structure):
+    """mirror of ``b200_rmsnorm_residual_args``"""
+    _fields_ = [("x", _vp), ("y1", _vp), ("s1", _f), ("y2", _vp), ("s2", _f),
+                ("expert_out", _vp), ("dest", _vp), ("weight", _vp), ("top", _i), ("bcast", _vp), ("rows", _vp),
+                ("w", _vp), ("w_offset", _f), ("eps", _f), ("out", _vp), ("out_dtype", _i), ("n_rows", _i), ("width", _i)]
+
+
+class ConvActArgs(C.Structure):
+    """mirror of ``b200_conv_act_args``"""
+    _fields_ = [("u", _vp), ("ld_u", _ll), ("w", _vp), ("bias", _vp), ("taps", _i), ("conv_state", _vp),
+                ("out32", _vp), ("out", _vp), ("out_dtype", _i), ("slot", _vp), ("pos", _vp), ("start", _vp),
+                ("n_tokens", _i), ("channels", _i), ("update_state_inline", _i)]
+
+
+class SelectiveScanArgs(C.Structure):
+    """mirror of ``b200_selective_scan_args``"""
+    _fields_ = [("x", _vp), ("dt_raw", _vp), ("dt_bias", _vp), ("B", _vp), ("C", _vp), ("ld_bc", _ll), ("z", _vp), ("ld_z", _ll),
+                ("A", _vp), ("D", _vp), ("state", _vp), ("out", _vp), ("out_dtype", _i),
+                ("ent_row", _vp), ("ent_len", _vp), ("slot", _vp), ("pos", _vp),
+                ("n_entries", _i), ("n_tokens", _i), ("channels", _i), ("n_state", _i), ("longest_entry", _i),
+                ("workspace", _vp), ("workspace_bytes", _sz)]
 
 
 class RetentionArgs(C.Structure):
@@ -78,6 +103,14 @@ SERVE_PROTOTYPES = {
     "b200_retention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "b200_retention": (_i, [C.POINTER(RetentionArgs), _vp]),
     "b200_unit_rms_gate": (_i, [_vp, _vp, _ll, _vp, _i, _i, _i, _f, _i, _vp]),
+    "b200_moe_route_logits": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "b200_rmsnorm_residual": (_i, [C.POINTER(RmsnormResidualArgs), _vp]),
+    "b200_rope_angles_amp": (_i, [_vp, _i, _vp, _i, C.c_double, _vp, _vp, _vp]),
+    "b200_diff_combine": (_i, [_vp, _f, _f, _f, _vp, _i, _i, _i, _i, _vp]),
+    "b200_sigmoid_gate": (_i, [_vp, _vp, _ll, _vp, _i, _i, _i, _vp]),
+    "b200_conv_act": (_i, [C.POINTER(ConvActArgs), _vp]),
+    "b200_selective_scan_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "b200_selective_scan": (_i, [C.POINTER(SelectiveScanArgs), _vp]),
     "b200_serve_last_error": (C.c_char_p, []),
     "b200_model_families": (C.c_char_p, []),
     "b200_model_open": (_vp, [C.c_char_p, C.POINTER(ModelOptions)]),
