@@ -55,16 +55,18 @@ struct Scan {
     float* state; void* out;
     const int* ent_row; const int* ent_len; const int* slot; const int* pos;
     int channels, n_state;
-    // chunk form: an entry's tokens [c0, c0 + len) with the state at c0 given by `carry`
-    int chunk; const int* chunk_ent; const int* chunk_first; float* summary;
+    // chunk form (entries of at least chunk_from tokens): chunk u covers tokens [chunk_first[u], + chunk) of entry chunk_ent[u]
+    int chunk, chunk_from; const int* chunk_ent; const int* chunk_first; float* summary;
 };
 
 constexpr int kScanThreads = 128, kScanPerLane = 8;
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-// MODE 0: the whole entry from the slot's state, which is left updated (decode steps, short portions).
-// MODE 1: one chunk from a zero state; leaves (sum of dt, local end state) per channel in `summary`, no outputs.
+// MODE 0: the whole entry from the slot's state, which is left updated (decode steps, short portions; entries that take
+//         the chunk form are skipped).
+// MODE 1: one chunk from a zero state; leaves (sum of dt, local end state) per channel in `summary`, no outputs (the last
+//         chunk of an entry has no successor and is skipped).
 // MODE 2: one chunk from the state that the chunk scan left at its start (summary holds it), with outputs; the last
 //         chunk of an entry stores the slot's state.
 template <typename T, int LP, int MODE>
@@ -79,13 +81,16 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
         e = blockIdx.y;
         row0 = a.ent_row[e];
         len = a.ent_len[e];
+        if (a.chunk > 0 && len >= a.chunk_from) return;
     } else {
         unit = blockIdx.y;
         e = a.chunk_ent[unit];
+        if (e < 0) return;
         const int off = a.chunk_first[unit], elen = a.ent_len[e];
         row0 = a.ent_row[e] + off;
         len = min(a.chunk, elen - off);
         last_chunk = off + len >= elen;
+        if (MODE == 1 && last_chunk) return;
     }
     first_pos = a.pos[row0];
     const int b = a.slot[row0];
@@ -243,11 +248,39 @@ extern "C" int b200_selective_scan(const b200_selective_scan_args* p, void* stre
     if (p->n_state > 32 * kScanPerLane) return B200_EUNSUPPORTED;
     if (p->out_dtype != B200_BF16 && p->out_dtype != B200_F32) return B200_EINVAL;
     if (p->n_entries == 0 || p->n_tokens == 0) return B200_OK;
+    if (p->n_entries > 65535) return B200_EUNSUPPORTED;
     Scan a{p->x, p->dt_raw, p->dt_bias, p->B, p->C, p->ld_bc, p->z, p->ld_z, p->A, p->D, p->state, p->out,
-           p->ent_row, p->ent_len, p->slot, p->pos, p->channels, p->n_state, 0, nullptr, nullptr, nullptr};
+           p->ent_row, p->ent_len, p->slot, p->pos, p->channels, p->n_state, 0, 0, nullptr, nullptr, nullptr};
     const int lp = scan_lanes(p->n_state);
     cudaStream_t s = (cudaStream_t)stream;
-    if (p->out_dtype == B200_BF16) scan_dispatch<__nv_bfloat16, 0>(a, lp, p->n_entries, s);
+    // long entries: chunk-local scans in parallel, a walk over the chunk summaries, then every chunk again from its true start
+    const size_t need = b200_selective_scan_workspace_bytes(p->n_tokens, p->n_entries, p->channels, p->n_state);
+    const size_t max_chunks = scan_max_chunks(p->n_tokens, p->n_entries);
+    const bool chunked = p->longest_entry >= kScanChunkFrom && need > 0 && p->workspace && p->workspace_bytes >= need && max_chunks <= 65535;
+    int* ent_chunk0 = nullptr;
+    if (chunked) {
+        a.chunk = kScanChunk;
+        a.chunk_from = kScanChunkFrom;
+        a.summary = reinterpret_cast<float*>(p->workspace);
+        int* tables = reinterpret_cast<int*>(a.summary + max_chunks * p->channels * (p->n_state + 1));
+        a.chunk_ent = tables;
+        a.chunk_first = tables + max_chunks;
+        ent_chunk0 = tables + 2 * max_chunks;
+        scan_tables_kernel<<<1, 32, 0, s>>>(p->ent_len, p->n_entries, kScanChunk, kScanChunkFrom, tables, tables + max_chunks, ent_chunk0,
+                                            (int)max_chunks);
+        count_launch();
+    }
+    const bool bf = p->out_dtype == B200_BF16;
+    if (bf) scan_dispatch<__nv_bfloat16, 0>(a, lp, p->n_entries, s);
     else scan_dispatch<float, 0>(a, lp, p->n_entries, s);
+    if (chunked) {
+        if (bf) scan_dispatch<__nv_bfloat16, 1>(a, lp, (int)max_chunks, s);
+        else scan_dispatch<float, 1>(a, lp, (int)max_chunks, s);
+        const size_t cells = (size_t)p->n_entries * p->channels * p->n_state;
+        scan_carry_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(a, ent_chunk0, p->n_entries);
+        count_launch();
+        if (bf) scan_dispatch<__nv_bfloat16, 2>(a, lp, (int)max_chunks, s);
+        else scan_dispatch<float, 2>(a, lp, (int)max_chunks, s);
+    }
     return (int)cudaGetLastError();
 }

@@ -66,9 +66,9 @@ def rot_frequencies(rot, kind):
 
 def rotate_half(x, rot, kind):
     """x [T, heads, dim], positions 0..T-1: the first rot['dims'] dimensions of every head, i paired with i + dims/2"""
-    T, d = x.shape[0], rot["dims"]
-    if d == 0:
+    if not rot or not rot.get("dims"):
         return x
+    T, d = x.shape[0], rot["dims"]
     f, amp = rot_frequencies(rot, kind)
     ang = torch.arange(T, dtype=DT)[:, None] * f[None, :]
     c, s = (amp * torch.cos(ang))[:, None, :], (amp * torch.sin(ang))[:, None, :]
@@ -109,7 +109,7 @@ def plain_attention(h, mx, W, pre, eps):
     q = (h @ W[pre + "q"].T).reshape(T, H, d)
     k = (h @ W[pre + "k"].T).reshape(T, G, d)
     v = (h @ W[pre + "v"].T).reshape(T, G, dv)
-    q, k = rotate_half(q, mx["rot"], "ramp"), rotate_half(k, mx["rot"], "ramp")
+    q, k = rotate_half(q, mx.get("rot"), "ramp"), rotate_half(k, mx.get("rot"), "ramp")
     o = softmax_attention(q, expand_groups(k, H), expand_groups(v, H), mx["scale"], visible(T))
     return o.reshape(T, H * dv) @ W[pre + "o"].T
 
@@ -122,7 +122,7 @@ def differential_attention(h, mx, W, pre, eps):
     v = expand_groups((h @ W[pre + "v"].T).reshape(T, G, dv), H)
     maps = []
     for m in range(2):
-        qm, km = rotate_half(q[:, :, m], mx["rot"], "linear"), rotate_half(k[:, :, m], mx["rot"], "linear")
+        qm, km = rotate_half(q[:, :, m], mx.get("rot"), "linear"), rotate_half(k[:, :, m], mx.get("rot"), "linear")
         maps.append(softmax_attention(qm, expand_groups(km, H), v, mx["scale"], visible(T)))
     lam = torch.exp((W[pre + "lq1"] * W[pre + "lk1"]).sum()) - torch.exp((W[pre + "lq2"] * W[pre + "lk2"]).sum()) + mx["diff"]
     o = unit_rms(maps[0] - lam * maps[1], eps) * (1 - mx["diff"])
@@ -135,8 +135,8 @@ def gated_chunk_attention(h, mx, W, pre):
     q = (h @ W[pre + "q"].T).reshape(T, H, d)
     k = (h @ W[pre + "k"].T).reshape(T, G, d)
     v = (h @ W[pre + "v"].T).reshape(T, G, dv)
-    q, k = rotate_half(q, mx["rot"], "plain"), rotate_half(k, mx["rot"], "plain")
-    o = softmax_attention(q, expand_groups(k, H), expand_groups(v, H), mx["scale"], visible(T, mx["mask"]["size"]))
+    q, k = rotate_half(q, mx.get("rot"), "plain"), rotate_half(k, mx.get("rot"), "plain")
+    o = softmax_attention(q, expand_groups(k, H), expand_groups(v, H), mx["scale"], visible(T, (mx.get("mask") or {}).get("size")))
     o = o.reshape(T, H * dv) * torch.sigmoid(h @ W[pre + "g"].T)
     return o @ W[pre + "o"].T
 
@@ -238,3 +238,110 @@ def forward(cfg, W, tokens, keep_layers=False, dtype=DT):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(kept)) if keep_layers else logits
+
+
+class Oracle:
+    def __init__(self, cfg, w):
+        self.cfg, self.w = cfg, w
+
+    def forward(self, tokens, return_layers=False):
+        return forward(self.cfg, self.w, tokens, keep_layers=return_layers)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# small random models for the tests (weights rounded to bfloat16, as a checkpoint stores them)
+# ---------------------------------------------------------------------------------------------------------------
+def random_model(seed, width, vocab, layers, loop=None, logit_softcap=8.0, eps=1e-5):
+    """layers: dicts with type 'attention' | 'parallel' | 'attention_2', the attention's heads, kv_heads, dim, vdim and
+    optionally rot_dims, base, scale, scaling, chunk (parallel), diff (attention); the scan's inner, state, dt_rank, conv
+    and the two weights left_scale, right_scale (parallel); ff = None | int (dense) | (ff, experts, top)."""
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, s=None):
+        return (torch.randn(*shape, generator=g) * (s if s is not None else 1.0 / math.sqrt(shape[-1]))).to(torch.bfloat16).to(DT)
+
+    cfg = dict(architecture="Tomalix", vocab=vocab, width=width, norm=dict(eps=eps), layers=[])
+    if logit_softcap:
+        cfg["logit_softcap"] = logit_softcap
+    w = {"embed": rnd(vocab, width, s=1.0), "head": rnd(vocab, width), "final.norm": rnd(width, s=0.1)}
+    if loop:
+        cfg["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+        w["loop.step"] = rnd(loop[2], width, s=0.3)
+
+    def attention(sp, pre, gate):
+        H, G, d, dv = sp["heads"], sp["kv_heads"], sp["dim"], sp["vdim"]
+        maps = 2 if sp["type"] == "attention" else 1
+        mx = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=sp.get("scale", 1.0 / math.sqrt(d)))
+        rd = sp.get("rot_dims", d)
+        if rd:
+            mx["rot"] = dict(base=sp.get("base", 10000.0), dims=rd)
+            if sp.get("scaling"):
+                mx["rot"]["scaling"] = dict(sp["scaling"])
+        w[pre + "q"], w[pre + "k"], w[pre + "v"] = rnd(H * maps * d, width), rnd(G * maps * d, width), rnd(G * dv, width)
+        w[pre + "o"] = rnd(width, H * dv)
+        if gate:
+            w[pre + "g"] = rnd(H * dv, width)
+        return mx
+
+    for i, sp in enumerate(layers):
+        pre = "l%d." % i
+        w[pre + "norm1"] = rnd(width, s=0.1)
+        if sp["type"] == "parallel":
+            left = attention(sp, pre + "mix.left.", True)
+            if sp.get("chunk"):
+                left["mask"] = dict(size=sp["chunk"])
+            C, N, R, taps = sp["inner"], sp["state"], sp["dt_rank"], sp["conv"]
+            rp = pre + "mix.right."
+            w[rp + "in"], w[rp + "conv"], w[rp + "conv.b"] = rnd(2 * C, width), rnd(C, taps, s=0.5), rnd(C, s=0.2)
+            w[rp + "x"], w[rp + "dt"] = rnd(R + 2 * N, C), rnd(C, R)
+            w[rp + "dt.b"] = (torch.randn(C, generator=g) * 0.7 - 2.0).to(torch.bfloat16).to(DT)
+            w[rp + "A_log"] = torch.log(torch.rand(C, N, generator=g) * 3 + 0.05).to(torch.bfloat16).to(DT)
+            w[rp + "D"], w[rp + "o"] = rnd(C, s=1.0), rnd(width, C)
+            mx = dict(left=left, right=dict(inner=C, state=N, dt_rank=R, conv=taps), left_scale=sp.get("left_scale", 1.0),
+                      right_scale=sp.get("right_scale", 1.0))
+        else:
+            mx = attention(sp, pre + "mix.", False)
+            if sp["type"] == "attention":
+                mx["diff"] = sp.get("diff", 0.3)
+                for nm in ("lq1", "lk1", "lq2", "lk2"):
+                    w[pre + "mix." + nm] = rnd(sp["dim"], s=0.4)
+        ff = sp.get("ff")
+        if ff is None:
+            ml = None
+        else:
+            w[pre + "norm2"] = rnd(width, s=0.1)
+            if isinstance(ff, int):
+                ml = dict(kind="dense", ff=ff)
+                w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(ff, width), rnd(width, ff)
+            else:
+                f, E, top = ff
+                ml = dict(kind="moe", expert=dict(ff=f), router=dict(experts=E, top=top))
+                for e in range(E):
+                    w[pre + "mlp.e%d.up" % e], w[pre + "mlp.e%d.down" % e] = rnd(f, width), rnd(width, f)
+                w[pre + "mlp.router"], w[pre + "mlp.router.b"] = rnd(E, width, s=1.0), rnd(E, s=0.5)
+        cfg["layers"].append(dict(type=sp["type"], mixer=mx, mlp=ml))
+    return cfg, w
+
+
+def write_model(folder, cfg, w):
+    """config.json + model.safetensors with every tensor as bfloat16"""
+    import json
+    import os
+    import struct
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, off = {}, [], 0
+    for name, t in w.items():
+        raw = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = dict(dtype="BF16", shape=list(t.shape), data_offsets=[off, off + len(raw)])
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
