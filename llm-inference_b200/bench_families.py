@@ -24,6 +24,25 @@ MUSILORN_SIZES = {
 }
 
 
+def tomalix_layers(width, heads, kv_heads, dim, ff, chunk, **_):
+    """four layers: block-masked gated attention beside a scan with a dense feed-forward; plain attention with routed experts
+    (four of sixteen, the same feed-forward width per token); differential attention (half the heads, two maps each, values
+    twice as wide); plain attention with a dense feed-forward"""
+    return [
+        dict(type="parallel", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, chunk=chunk, inner=2 * width, state=16,
+             dt_rank=width // 16, conv=4, ff=ff),
+        dict(type="attention_2", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, ff=(ff // 4, 16, 4)),
+        dict(type="attention", heads=heads // 2, kv_heads=kv_heads // 2, dim=dim, vdim=2 * dim, ff=ff),
+        dict(type="attention_2", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, ff=ff),
+    ]
+
+
+TOMALIX_SIZES = {
+    "s": dict(width=1024, heads=8, kv_heads=4, dim=128, ff=4096, chunk=1024, n_layers=4, vocab=32000),
+    "m": dict(width=2048, heads=16, kv_heads=8, dim=128, ff=8192, chunk=1024, n_layers=4, vocab=32000),
+}
+
+
 def timed(fn, steps, warmup):
     import torch
     for _ in range(warmup):
@@ -41,6 +60,8 @@ def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, d
     import torch
 
     S, E, capi = pkg.serve, pkg.engine, pkg.capi
+    if family == "tomalix":
+        return run_tomalix(pkg, size, prompt, batch, context, steps, warmup, dtype)
     sz = (MUSILORN_SIZES if family == "musilorn" else SIZES)[size]
     rng = np.random.default_rng(0)
     out = {"workload": family, "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
@@ -102,4 +123,56 @@ def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, d
     except Exception as ex:   # the comparison must not take the family's own numbers down
         ll["failed"] = f"{type(ex).__name__}: {ex}"
     out["llama_equal_size"] = ll
+    return out
+
+
+def serve_family(S, cfg, w, prompt, batch, context, steps, warmup, dtype, vocab):
+    """prefill of one prompt and decode steps of `batch` sequences at `context` tokens through b200_model_step"""
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    with tempfile.TemporaryDirectory() as folder:
+        S.write_checkpoint(folder, cfg, w)
+        PR = 64
+        need = max(prompt + PR, batch * (context + steps + warmup + PR + 8))
+        m = S.Model(folder, dtype=S.BF16 if dtype == "bfloat16" else S.F32, max_tokens=need, max_slots=batch)
+    ids = rng.integers(0, vocab, prompt).tolist()
+    out = {}
+
+    def prefill():
+        m.step([(0, ids, [prompt - 1])], logits=False, ids=True)
+        m.release(0)
+    t = timed(prefill, steps, warmup)
+    out["prefill"] = {"tokens_per_s": prompt / t, "ms": t * 1e3, "launches": m.step_launches}
+    for b in range(batch):
+        m.step([(b, rng.integers(0, vocab, context).tolist(), [])], logits=False)
+    tok = rng.integers(0, vocab, batch).tolist()
+
+    def decode():
+        m.step([(b, [tok[b]], [0]) for b in range(batch)], logits=False, ids=True)
+    t = timed(decode, steps, warmup)
+    out["decode"] = {"tokens_per_s": batch / t, "ms": t * 1e3, "launches": m.step_launches}
+    m.close()
+    return out
+
+
+def run_tomalix(pkg, size, prompt, batch, context, steps, warmup, dtype):
+    """The Tomalix family beside the closest existing one, Musilorn (the same serving layer, paged attention, a recurrent
+    layer with carried state, fp32 residual), at equal width, heads, feed-forward width per token, layer count and vocabulary."""
+    S = pkg.serve
+    sz = TOMALIX_SIZES[size]
+    out = {"workload": "tomalix", "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
+           "dtype": dtype, "data": "synthetic ids, random weights", "timing": "host clock around synchronous steps (each step ends "
+           "with the device-to-host copy of its results), after warm-up"}
+    cfg, w = S.random_tomalix(sz["width"], sz["vocab"], tomalix_layers(**sz))
+    out.update(serve_family(S, cfg, w, prompt, batch, context, steps, warmup, dtype, sz["vocab"]))
+    del w
+    mu = dict(MUSILORN_SIZES[size])
+    try:
+        cfg, w = S.random_musilorn(**mu)
+        res = serve_family(S, cfg, w, prompt, batch, context, steps, warmup, dtype, mu["vocab"])
+        res["shape"] = mu
+        out["musilorn_equal_size"] = res
+    except Exception as ex:   # the comparison must not take the family's own numbers down
+        out["musilorn_equal_size"] = {"failed": f"{type(ex).__name__}: {ex}"}
     return out

@@ -379,17 +379,18 @@ __device__ __forceinline__ uint32_t pa_pack(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D>   // dim == vdim == D
-__global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(const PA a) {
+template <int D, int DV>   // dim == D (a multiple of 32), vdim == DV (a multiple of 16)
+__global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel(const PA a) {
     using bf = __nv_bfloat16;
     constexpr int RS = D + 8;                 // row stride in elements: 16-byte aligned, conflict-free fragment loads
     constexpr int CH = D / 8;                 // 16-byte chunks per row
+    constexpr int RSV = DV + 8, CHV = DV / 8; // the same for value rows
     extern __shared__ __align__(16) unsigned char pa_smem[];
     bf* Ks = reinterpret_cast<bf*>(pa_smem);                  // [2][64][RS]
-    bf* Vs = Ks + 2 * kTileN * RS;                            // [2][64][RS]
+    bf* Vs = Ks + 2 * kTileN * RS;                            // [2][64][RSV]
     bf* Qs = Ks + kTileN * RS;                                // [64][RS]: the Q tile borrows the second K buffer until its
                                                               // fragments are in registers (three CTAs fit an SM this way)
-    int* row_pos = reinterpret_cast<int*>(Vs + 2 * kTileN * RS);   // [64], -1: no such row
+    int* row_pos = reinterpret_cast<int*>(Vs + 2 * kTileN * RSV);   // [64], -1: no such row
     int* row_slot = row_pos + kTileM;
     // the last rows of a prompt see the most keys: those tiles are scheduled first, the short ones fill the tail
     const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTileM, h = blockIdx.y;   // h: query unit (head, map)
@@ -413,9 +414,9 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks)
         pa_ldsm_x4(qf[ks], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + ks * 16 + (lane >> 4) * 8);
-    float o[D / 8][4];
+    float o[DV / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    for (int nt = 0; nt < DV / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
     const float m0 = a.denom_bias > 0.f ? 0.f : -1e30f;
     float m_run[2] = {m0, m0}, l_run[2] = {a.denom_bias, a.denom_bias};
     const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;
@@ -439,16 +440,19 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
         const int warp_first = w_last >= w_first ? pa_first_key(a, row_pos[w_first]) : 0;
         auto load_tile = [&](int k0, int buf) {
             bf* kd = Ks + buf * kTileN * RS;
-            bf* vd = Vs + buf * kTileN * RS;
-            for (int i = threadIdx.x; i < kTileN * CH; i += blockDim.x) {
-                const int kr = i / CH, c = i % CH, j = k0 + kr;
+            bf* vd = Vs + buf * kTileN * RSV;
+            for (int i = threadIdx.x; i < kTileN * (CH + CHV); i += blockDim.x) {
+                const int kr = i / (CH + CHV), c = i % (CH + CHV), j = k0 + kr;
                 const bool ok = j < n_keys;
                 const size_t row = ok ? (size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows : 0;
                 const uint32_t bytes = ok ? 16u : 0u;                 // beyond the sequence: zeros, nothing is read
-                const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(kd + kr * RS + c * 8);
-                const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(vd + kr * RS + c * 8);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + (row * k_units + ku) * D + c * 8), "r"(bytes) : "memory");
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + (row * a.kv_heads + g) * D + c * 8), "r"(bytes) : "memory");
+                if (c < CH) {
+                    const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(kd + kr * RS + c * 8);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + (row * k_units + ku) * D + c * 8), "r"(bytes) : "memory");
+                } else {
+                    const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(vd + kr * RSV + (c - CH) * 8);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + (row * a.kv_heads + g) * DV + (c - CH) * 8), "r"(bytes) : "memory");
+                }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
@@ -461,7 +465,7 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
             if (k0 + kTileN < n_keys) load_tile(k0 + kTileN, buf ^ 1);
             if (k0 >= warp_keys || k0 + kTileN <= warp_first) continue;   // nothing for this warp's rows in this tile (it keeps the barriers)
             const bf* Kb = Ks + buf * kTileN * RS;
-            const bf* Vb = Vs + buf * kTileN * RS;
+            const bf* Vb = Vs + buf * kTileN * RSV;
             float s[kTileN / 8][4];
 #pragma unroll
             for (int nt = 0; nt < kTileN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -551,7 +555,7 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
                 l_run[hrow] = l_run[hrow] * alpha[hrow] + sum[hrow];
             }
 #pragma unroll
-            for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
+            for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
 #pragma unroll
             for (int kk = 0; kk < kTileN / 16; ++kk) {
                 uint32_t pf[4];
@@ -560,9 +564,9 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
                 pf[2] = pa_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
                 pf[3] = pa_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-                for (int nt = 0; nt < D / 8; nt += 2) {   // one transposed ldmatrix.x4: the V fragments of two column tiles
+                for (int nt = 0; nt < DV / 8; nt += 2) {   // one transposed ldmatrix.x4: the V fragments of two column tiles
                     uint32_t b4[4];
-                    pa_ldsm_x4_trans(b4, Vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + (nt + (lane >> 4)) * 8);
+                    pa_ldsm_x4_trans(b4, Vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RSV + (nt + (lane >> 4)) * 8);
                     const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
                     pa_mma(o[nt], pf, b0);
                     pa_mma(o[nt + 1], pf, b1);
@@ -576,28 +580,34 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
         const int r = hrow ? r_hi : r_lo;
         if (r >= rows) continue;
         const float inv = 1.0f / l_run[hrow];
-        const size_t dst = ((size_t)(t0 + r) * q_units + h) * D + tig * 2;
+        const size_t dst = ((size_t)(t0 + r) * q_units + h) * DV + tig * 2;
         if (a.out_f32) {
 #pragma unroll
-            for (int nt = 0; nt < D / 8; ++nt)
+            for (int nt = 0; nt < DV / 8; ++nt)
                 *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + dst + nt * 8) = make_float2(o[nt][hrow * 2] * inv, o[nt][hrow * 2 + 1] * inv);
         } else {
 #pragma unroll
-            for (int nt = 0; nt < D / 8; ++nt)
+            for (int nt = 0; nt < DV / 8; ++nt)
                 *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf*>(a.out) + dst + nt * 8) = __floats2bfloat162_rn(o[nt][hrow * 2] * inv, o[nt][hrow * 2 + 1] * inv);
         }
     }
 }
 
-template <int D>
+template <int D, int DV>
 static int launch_tile(const PA& a, cudaStream_t s) {
     static_assert(kTileM == kTileN, "the Q tile borrows a K buffer");
-    constexpr int smem = 4 * kTileN * (D + 8) * 2 + 2 * kTileM * 4;
+    constexpr int smem = 2 * kTileN * (D + 8) * 2 + 2 * kTileN * (DV + 8) * 2 + 2 * kTileM * 4;
     static unsigned long long done = 0;
-    const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D>, smem, done);
+    const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D, DV>, smem, done);
     if (e != cudaSuccess) return (int)e;
-    paged_attn_tile_kernel<D><<<dim3((a.n_tokens + kTileM - 1) / kTileM, a.heads * a.maps), 128, smem, s>>>(a);
+    paged_attn_tile_kernel<D, DV><<<dim3((a.n_tokens + kTileM - 1) / kTileM, a.heads * a.maps), 128, smem, s>>>(a);
     return (int)cudaGetLastError();
+}
+// the (dim, vdim) pairs the tile kernel is built for: equal sizes, and values twice as wide as the keys
+static int launch_tile_for(const PA& a, cudaStream_t s) {
+    if (a.dim == a.vdim) return a.dim == 128 ? launch_tile<128, 128>(a, s) : a.dim == 64 ? launch_tile<64, 64>(a, s) : a.dim == 32 ? launch_tile<32, 32>(a, s) : -1;
+    if (a.vdim == 2 * a.dim) return a.dim == 128 ? launch_tile<128, 256>(a, s) : a.dim == 64 ? launch_tile<64, 128>(a, s) : a.dim == 32 ? launch_tile<32, 64>(a, s) : -1;
+    return -1;
 }
 
 }  // namespace b200
@@ -624,11 +634,12 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     const char* env = getenv("B200_ATTN_ROWS");   // 1: every batch on the row kernel (debugging aid)
-    if (p->dtype == B200_BF16 && p->longest_entry != 1 && p->dim == p->vdim && (p->dim == 64 || p->dim == 128 || p->dim == 32) &&
-        al16(p->q) && al16(p->out) && al16(p->k_pool) && al16(p->v_pool) && !(env && env[0] == '1')) {
-        const int rc = p->dim == 128 ? launch_tile<128>(a, s) : p->dim == 64 ? launch_tile<64>(a, s) : launch_tile<32>(a, s);
+    if (p->dtype == B200_BF16 && p->longest_entry != 1 && (p->dim == p->vdim || p->vdim == 2 * p->dim) &&
+        (p->dim == 64 || p->dim == 128 || p->dim == 32) && al16(p->q) && al16(p->out) && al16(p->k_pool) && al16(p->v_pool) &&
+        !(env && env[0] == '1')) {
+        const int rc = launch_tile_for(a, s);
         if (rc == 0) count_launch();
-        return rc;
+        if (rc >= 0) return rc;
     }
     // single tokens whose heads come in groups of 1, 2, 4 or 8 per key head: one pass over K / V serves the whole group
     const int R = p->heads / p->kv_heads;

@@ -66,6 +66,79 @@ __global__ void __launch_bounds__(kRnThreads) rmsnorm_residual_kernel(const RnAr
     for (int c = threadIdx.x; c < width; c += kRnThreads) out[c] = DT<T>::from_f(rn_row[c] * rinv * (a.w_offset + a.w[c]));
 }
 
+// The same for rows of at most 8 values per thread: every operand of the row is loaded up front (one round trip to memory
+// instead of a dependent chain per column) and the row lives in registers.
+constexpr int kRnPer = 8;
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) rmsnorm_residual_reg_kernel(const RnArgs a) {
+    __shared__ float red[THREADS / 32];
+    __shared__ int e_dest[kRnMaxTop];
+    __shared__ float e_w[kRnMaxTop];
+    const int i = blockIdx.x, width = a.width;
+    const size_t src = (size_t)(a.rows ? a.rows[i] : i) * width;
+    const bool adds = !a.rows && (a.y1 || a.y2 || a.eo || a.bcast);
+    if (a.eo && threadIdx.x < a.top) {
+        e_dest[threadIdx.x] = a.dest[(size_t)i * a.top + threadIdx.x];
+        e_w[threadIdx.x] = a.weight[(size_t)i * a.top + threadIdx.x];
+    }
+    if (a.eo) __syncthreads();
+    float v[kRnPer], p1[kRnPer], p2[kRnPer], pb[kRnPer], wv[kRnPer];
+#pragma unroll
+    for (int k = 0; k < kRnPer; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        const bool in = c < width;
+        v[k] = in ? a.x[src + c] : 0.f;
+        p1[k] = (in && adds && a.y1) ? a.y1[src + c] : 0.f;
+        p2[k] = (in && adds && a.y2) ? a.y2[src + c] : 0.f;
+        pb[k] = (in && adds && a.bcast) ? a.bcast[c] : 0.f;
+        wv[k] = (in && a.w) ? a.w[c] : 0.f;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kRnPer; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        if (adds && c < width) {
+            // the order of the plain kernel: y1, y2, experts, the shared vector
+            if (a.y1) v[k] += a.s1 * p1[k];
+            if (a.y2) v[k] += a.s2 * p2[k];
+            if (a.eo) {
+                float r = 0.f;
+                for (int j = 0; j < a.top; ++j)
+                    if (e_dest[j] >= 0) r = fmaf(e_w[j], a.eo[(size_t)e_dest[j] * width + c], r);
+                v[k] += r;
+            }
+            if (a.bcast) v[k] += pb[k];
+            a.x[src + c] = v[k];
+        }
+        ss += v[k] * v[k];
+    }
+    if (!a.w) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < THREADS / 32; ++k) tot += red[k];
+    const float rinv = 1.0f / sqrtf(tot / (float)width + a.eps);
+    T* out = reinterpret_cast<T*>(a.out) + (size_t)i * width;
+#pragma unroll
+    for (int k = 0; k < kRnPer; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        if (c < width) out[c] = DT<T>::from_f(v[k] * rinv * (a.w_offset + wv[k]));
+    }
+}
+
+template <typename T>
+static void launch_rn(const RnArgs& a, int n_rows, size_t smem, cudaStream_t s) {
+    if (a.width <= 256 * kRnPer) rmsnorm_residual_reg_kernel<T, 256><<<n_rows, 256, 0, s>>>(a);
+    else if (a.width <= 1024 * kRnPer) rmsnorm_residual_reg_kernel<T, 1024><<<n_rows, 1024, 0, s>>>(a);
+    else {
+        static unsigned long long done = 0;
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)rmsnorm_residual_kernel<T>, 200 * 1024, done);
+        rmsnorm_residual_kernel<T><<<n_rows, kRnThreads, smem, s>>>(a);
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -82,16 +155,9 @@ extern "C" int b200_rmsnorm_residual(const b200_rmsnorm_residual_args* p, void* 
     RnArgs a{p->x, p->y1, p->s1, p->y2, p->s2, p->expert_out, p->dest, p->weight, p->top, p->bcast, p->rows, p->w, p->w_offset, p->eps,
              p->out, p->width};
     cudaStream_t s = (cudaStream_t)stream;
-    if (p->out_dtype == B200_BF16 || !p->w) {
-        static unsigned long long done = 0;
-        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)rmsnorm_residual_kernel<__nv_bfloat16>, 200 * 1024, done);
-        rmsnorm_residual_kernel<__nv_bfloat16><<<p->n_rows, kRnThreads, smem, s>>>(a);
-    } else if (p->out_dtype == B200_F32) {
-        static unsigned long long done = 0;
-        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)rmsnorm_residual_kernel<float>, 200 * 1024, done);
-        rmsnorm_residual_kernel<float><<<p->n_rows, kRnThreads, smem, s>>>(a);
-    } else
-        return B200_EINVAL;
+    if (p->out_dtype == B200_BF16 || !p->w) launch_rn<__nv_bfloat16>(a, p->n_rows, smem, s);
+    else if (p->out_dtype == B200_F32) launch_rn<float>(a, p->n_rows, smem, s);
+    else return B200_EINVAL;
     count_launch();
     return (int)cudaGetLastError();
 }

@@ -59,7 +59,7 @@ struct Scan {
     int chunk, chunk_from; const int* chunk_ent; const int* chunk_first; float* summary;
 };
 
-constexpr int kScanThreads = 128, kScanPerLane = 8;
+constexpr int kScanThreads = 128, kScanPerLane = 8, kScanGroup = 4;
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
@@ -107,27 +107,41 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
     }
     const float dtb = a.dt_bias ? a.dt_bias[cc] : 0.f, Dc = a.D ? a.D[cc] : 0.f;
     float dt_sum = 0.f;
-    for (int i = 0; i < len; ++i) {
-        const size_t t = (size_t)row0 + i;
-        const float dt = softplus_f(a.dt_raw[t * Cn + cc] + dtb), xv = a.x[t * Cn + cc];
-        const float* Bt = a.B + t * a.ld_bc;
-        const float* Ct = a.C + t * a.ld_bc;
-        const float dx = dt * xv;
-        float y = 0.f;
+    // tokens in groups of kScanGroup: every operand of the group is loaded before the first update, so the walk pays one
+    // round trip to memory per group and not one per token
+    for (int i0 = 0; i0 < len; i0 += kScanGroup) {
+        float dtr[kScanGroup], xv[kScanGroup], zv[kScanGroup], Bv[kScanGroup][kScanPerLane], Cv[kScanGroup][kScanPerLane];
 #pragma unroll
-        for (int k = 0; k < kScanPerLane; ++k) {
-            const int n = lane + k * LP;
-            if (n < N) {
-                S[k] = fmaf(expf(dt * Av[k]), S[k], dx * Bt[n]);
-                if (MODE != 1) y = fmaf(S[k], Ct[n], y);
+        for (int j = 0; j < kScanGroup; ++j) {
+            const bool in = i0 + j < len;
+            const size_t t = (size_t)row0 + (in ? i0 + j : 0);
+            dtr[j] = in ? __ldg(a.dt_raw + t * Cn + cc) : 0.f;
+            xv[j] = in ? __ldg(a.x + t * Cn + cc) : 0.f;
+            zv[j] = (MODE != 1 && in && lane == 0) ? __ldg(a.z + t * a.ld_z + cc) : 0.f;
+#pragma unroll
+            for (int k = 0; k < kScanPerLane; ++k) {
+                const int n = lane + k * LP;
+                Bv[j][k] = (in && n < N) ? __ldg(a.B + t * a.ld_bc + n) : 0.f;
+                Cv[j][k] = (MODE != 1 && in && n < N) ? __ldg(a.C + t * a.ld_bc + n) : 0.f;
             }
         }
-        if (MODE == 1) { dt_sum += dt; continue; }
 #pragma unroll
-        for (int o = LP / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (lane == 0 && live) {
-            const float zv = a.z[t * a.ld_z + cc];
-            reinterpret_cast<T*>(a.out)[t * Cn + cc] = DT<T>::from_f((y + Dc * xv) * (zv / (1.f + expf(-zv))));
+        for (int j = 0; j < kScanGroup; ++j) {
+            if (i0 + j >= len) break;
+            const float dt = softplus_f(dtr[j] + dtb), dx = dt * xv[j];
+            float y = 0.f;
+#pragma unroll
+            for (int k = 0; k < kScanPerLane; ++k) {
+                if (lane + k * LP < N) {
+                    S[k] = fmaf(expf(dt * Av[k]), S[k], dx * Bv[j][k]);
+                    if (MODE != 1) y = fmaf(S[k], Cv[j][k], y);
+                }
+            }
+            if (MODE == 1) { dt_sum += dt; continue; }
+#pragma unroll
+            for (int o = LP / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (lane == 0 && live)
+                reinterpret_cast<T*>(a.out)[((size_t)row0 + i0 + j) * Cn + cc] = DT<T>::from_f((y + Dc * xv[j]) * (zv[j] / (1.f + expf(-zv[j]))));
         }
     }
     if (!live) return;
@@ -160,11 +174,20 @@ __global__ void __launch_bounds__(256) scan_carry_kernel(const Scan a, const int
     const int row0 = a.ent_row[e];
     const float Av = a.A[(size_t)c * N + n];
     float S = a.pos[row0] > 0 ? a.state[((size_t)a.slot[row0] * Cn + c) * N + n] : 0.f;
-    for (int u = u0; u < u1; ++u) {
-        float* sm = a.summary + ((size_t)u * Cn + c) * (N + 1);
-        const float local = sm[1 + n];
-        sm[1 + n] = S;
-        S = fmaf(expf(Av * sm[0]), S, local);
+    for (int g0 = u0; g0 < u1; g0 += 4) {   // the loads of four chunks in flight together
+        float local[4], dts[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float* sm = a.summary + ((size_t)min(g0 + j, u1 - 1) * Cn + c) * (N + 1);
+            local[j] = sm[1 + n];
+            dts[j] = sm[0];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (g0 + j >= u1) break;
+            a.summary[((size_t)(g0 + j) * Cn + c) * (N + 1) + 1 + n] = S;
+            S = fmaf(expf(Av * dts[j]), S, local[j]);
+        }
     }
 }
 

@@ -349,3 +349,70 @@ def random_musilorn(width, heads, kv_heads, dim, ff, n_layers, vocab, retention_
         w[pre + "mlp.gate"], w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(ff, width), rnd(ff, width), rnd(width, ff)
         cfg["layers"].append(dict(type="attention", mixer=mx, mlp=dict(kind="dense", ff=ff)))
     return cfg, w
+
+
+def random_tomalix(width, vocab, layers, loop=None, seed=0):
+    """(config, tensors) of a random Tomalix model. layers: dicts with type 'attention' (differential) | 'parallel' |
+    'attention_2', heads, kv_heads, dim, vdim, optionally chunk (parallel) and the scan's inner, state, dt_rank, conv;
+    ff = None | int (dense) | (ff, experts, top); `loop` = (start, stop, times) or None"""
+    import math
+
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, s=None):
+        return (torch.randn(*shape, generator=g) * (s if s is not None else 1.0 / math.sqrt(shape[-1]))).to(torch.bfloat16)
+
+    cfg = dict(architecture="Tomalix", vocab=vocab, width=width, norm=dict(eps=1e-5), logit_softcap=30.0, layers=[])
+    w = {"embed": rnd(vocab, width, s=1.0), "head": rnd(vocab, width), "final.norm": torch.zeros(width)}
+    if loop:
+        cfg["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+        w["loop.step"] = rnd(loop[2], width, s=0.1)
+    for i, sp in enumerate(layers):
+        pre = f"l{i}."
+        H, G, d, dv = sp["heads"], sp["kv_heads"], sp["dim"], sp["vdim"]
+        kind = sp["type"]
+        maps = 2 if kind == "attention" else 1
+        ap = pre + ("mix.left." if kind == "parallel" else "mix.")
+        att = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=1.0 / math.sqrt(d), rot=dict(base=500000.0, dims=d))
+        w[ap + "q"], w[ap + "k"], w[ap + "v"] = rnd(H * maps * d, width), rnd(G * maps * d, width), rnd(G * dv, width)
+        w[ap + "o"] = rnd(width, H * dv)
+        w[pre + "norm1"] = torch.zeros(width)
+        if kind == "parallel":
+            w[ap + "g"] = rnd(H * dv, width)
+            if sp.get("chunk"):
+                att["mask"] = dict(size=sp["chunk"])
+            C_, N, R, taps = sp["inner"], sp["state"], sp["dt_rank"], sp["conv"]
+            rp = pre + "mix.right."
+            w[rp + "in"], w[rp + "conv"], w[rp + "conv.b"] = rnd(2 * C_, width), rnd(C_, taps, s=0.5), torch.zeros(C_)
+            w[rp + "x"], w[rp + "dt"] = rnd(R + 2 * N, C_), rnd(C_, R)
+            w[rp + "dt.b"] = torch.full((C_,), -3.0)
+            w[rp + "A_log"] = torch.log(torch.arange(1, N + 1, dtype=torch.float32)).repeat(C_, 1)
+            w[rp + "D"], w[rp + "o"] = torch.ones(C_), rnd(width, C_)
+            mx = dict(left=att, right=dict(inner=C_, state=N, dt_rank=R, conv=taps), left_scale=1.0, right_scale=1.0)
+        else:
+            mx = att
+            if kind == "attention":
+                mx["diff"] = 0.3
+                mx["rot"]["scaling"] = dict(factor=4.0)
+                for nm in ("lq1", "lk1", "lq2", "lk2"):
+                    w[pre + "mix." + nm] = rnd(d, s=0.1)
+            else:
+                mx["rot"]["scaling"] = dict(factor=8.0, original=8192, fast=32.0, slow=1.0)
+        ff = sp.get("ff")
+        if ff is None:
+            ml = None
+        else:
+            w[pre + "norm2"] = torch.zeros(width)
+            if isinstance(ff, int):
+                ml = dict(kind="dense", ff=ff)
+                w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(ff, width), rnd(width, ff)
+            else:
+                f, E, top = ff
+                ml = dict(kind="moe", expert=dict(ff=f), router=dict(experts=E, top=top))
+                for e in range(E):
+                    w[pre + f"mlp.e{e}.up"], w[pre + f"mlp.e{e}.down"] = rnd(f, width), rnd(width, f)
+                w[pre + "mlp.router"], w[pre + "mlp.router.b"] = rnd(E, width), torch.zeros(E)
+        cfg["layers"].append(dict(type=kind, mixer=mx, mlp=ml))
+    return cfg, w

@@ -70,7 +70,7 @@ def ptr(t):
 
 # ---------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("kind", ["f32", "bf16"])
-@pytest.mark.parametrize("width", [1, 5, 48, 300, 5000])
+@pytest.mark.parametrize("width", [1, 5, 48, 300, 2048, 5000, 9000])
 def test_residual_update_with_the_next_norm(S, width, kind):
     code, g, T, top = code_of(S, kind), gen(width), 7, 3
     x, y1, y2 = (torch.randn(T, width, generator=g) for _ in range(3))
