@@ -46,10 +46,11 @@ int b200_layernorm_pair(const float* x, const int* rows, int n_rows, int width, 
 #define B200_GG_GLU 2         /* C = silu(A W[0:N]^T) * (A W[N:2N]^T); W has 2N rows; trans_b only  */
 #define B200_GG_GLU_GELU 3    /* the same with gelu in its tanh form as the activation              */
 #define B200_GG_RELU2 4       /* C = max(acc, 0)^2                                                   */
+#define B200_GG_BIAS_SOFTPLUS 5 /* C = log(1 + exp(acc + aux[row, col])); ld_aux 0: a bias per column */
 
 typedef struct b200_gemm_grouped_args {
     const void* A; const void* W; void* C;
-    const float* aux;          /* SIGMOID_MUL: fp32 [rows, ld_aux] (+ batch * stride_aux)                       */
+    const float* aux;          /* SIGMOID_MUL, BIAS_SOFTPLUS: fp32 [rows, ld_aux] (+ batch * stride_aux)        */
     const int* a_rows;         /* device: source row of A for each logical row (NULL = identity)               */
     const int* group_off;      /* device [batch + 1]: group g owns logical rows [off[g], off[g+1]) (NULL = none) */
     long long lda, ldw, ldc, ld_aux;                       /* leading dimensions in elements                   */
@@ -253,7 +254,8 @@ int b200_sigmoid_gate(const float* o, const float* gate, long long ld_gate, void
  * next projection) may each be NULL.
  *
  * b200_selective_scan: per entry (a run of consecutive tokens of one sequence), channel c and state n, with
- * dt = softplus(dt_raw[t, c] + dt_bias[c]):
+ * dt = softplus(dt_raw[t, c] + dt_bias[c]) (or dt = dt_raw[t, c] as it is when dt_ready != 0: the caller's projection
+ * has applied bias and softplus already):
  *   S[c, n] <- exp(dt * A[c, n]) * S[c, n] + dt * x[t, c] * B[t, n];   y = sum_n S[c, n] * C[t, n] + D[c] * x[t, c]
  *   out[t, c] = y * silu(z[t, c])        (as out_dtype)
  * A fp32 [channels, n_state] (already negative), S fp32 [n_slots, channels, n_state], starting from zero when the entry
@@ -276,6 +278,7 @@ typedef struct b200_selective_scan_args {
     const int* ent_row; const int* ent_len; const int* slot; const int* pos;
     int n_entries, n_tokens, channels, n_state, longest_entry;
     void* workspace; size_t workspace_bytes;   /* chunk summaries of long entries (b200_selective_scan_workspace_bytes) */
+    int dt_ready;
 } b200_selective_scan_args;
 size_t b200_selective_scan_workspace_bytes(int n_tokens, int n_entries, int channels, int n_state);
 int b200_selective_scan(const b200_selective_scan_args* a, void* stream);

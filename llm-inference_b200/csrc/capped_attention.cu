@@ -379,12 +379,12 @@ __device__ __forceinline__ uint32_t pa_pack(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D, int DV>   // dim == D (a multiple of 32), vdim == DV (a multiple of 16)
+template <int D, int DV, bool BLOCKS>   // dim == D (a multiple of 32), vdim == DV (a multiple of 16); BLOCKS: a.chunk > 0
 __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel(const PA a) {
     using bf = __nv_bfloat16;
     constexpr int RS = D + 8;                 // row stride in elements: 16-byte aligned, conflict-free fragment loads
     constexpr int CH = D / 8;                 // 16-byte chunks per row
-    constexpr int RSV = DV + 8, CHV = DV / 8; // the same for value rows
+    constexpr int RSV = DV + 8;               // the same for value rows
     extern __shared__ __align__(16) unsigned char pa_smem[];
     bf* Ks = reinterpret_cast<bf*>(pa_smem);                  // [2][64][RS]
     bf* Vs = Ks + 2 * kTileN * RS;                            // [2][64][RSV]
@@ -429,29 +429,30 @@ __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel
         int seg_end = seg + 1;
         while (seg_end < rows && row_slot[seg_end] == b) ++seg_end;
         const int n_keys = row_pos[seg_end - 1] + 1;            // positions grow along an entry
-        const int first_key = pa_first_key(a, row_pos[seg]);    // with a block mask the first row's block starts the walk
+        const int first_key = BLOCKS ? pa_first_key(a, row_pos[seg]) : 0;    // with a block mask the first row's block starts the walk
         const int* plist = a.pages + (size_t)b * a.max_pages;
         // this thread's two rows in this segment (last and first key each sees), and the keys any row of the warp sees
         const int p_lo = (r_lo >= seg && r_lo < seg_end) ? row_pos[r_lo] : -1;
         const int p_hi = (r_hi >= seg && r_hi < seg_end) ? row_pos[r_hi] : -1;
-        const int f_lo = p_lo >= 0 ? pa_first_key(a, p_lo) : 0, f_hi = p_hi >= 0 ? pa_first_key(a, p_hi) : 0;
+        const int f_lo = (BLOCKS && p_lo >= 0) ? pa_first_key(a, p_lo) : 0, f_hi = (BLOCKS && p_hi >= 0) ? pa_first_key(a, p_hi) : 0;
         const int w_first = max(seg, warp * 16), w_last = min(seg_end, warp * 16 + 16) - 1;
         const int warp_keys = w_last >= w_first ? row_pos[w_last] + 1 : 0;
-        const int warp_first = w_last >= w_first ? pa_first_key(a, row_pos[w_first]) : 0;
+        const int warp_first = (BLOCKS && w_last >= w_first) ? pa_first_key(a, row_pos[w_first]) : 0;
         auto load_tile = [&](int k0, int buf) {
             bf* kd = Ks + buf * kTileN * RS;
             bf* vd = Vs + buf * kTileN * RSV;
-            for (int i = threadIdx.x; i < kTileN * (CH + CHV); i += blockDim.x) {
-                const int kr = i / (CH + CHV), c = i % (CH + CHV), j = k0 + kr;
+            // a thread brings chunk c of key row kr, and the DV / D value chunks that go with it (one page lookup for all)
+            for (int i = threadIdx.x; i < kTileN * CH; i += blockDim.x) {
+                const int kr = i / CH, c = i % CH, j = k0 + kr;
                 const bool ok = j < n_keys;
                 const size_t row = ok ? (size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows : 0;
                 const uint32_t bytes = ok ? 16u : 0u;                 // beyond the sequence: zeros, nothing is read
-                if (c < CH) {
-                    const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(kd + kr * RS + c * 8);
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + (row * k_units + ku) * D + c * 8), "r"(bytes) : "memory");
-                } else {
-                    const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(vd + kr * RSV + (c - CH) * 8);
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + (row * a.kv_heads + g) * DV + (c - CH) * 8), "r"(bytes) : "memory");
+                const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(kd + kr * RS + c * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + (row * k_units + ku) * D + c * 8), "r"(bytes) : "memory");
+#pragma unroll
+                for (int e = 0; e < DV / D; ++e) {
+                    const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(vd + kr * RSV + (c + e * CH) * 8);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + (row * a.kv_heads + g) * DV + (c + e * CH) * 8), "r"(bytes) : "memory");
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();   // tile k0 has landed for everybody; the other buffer is no longer read
             if (k0 + kTileN < n_keys) load_tile(k0 + kTileN, buf ^ 1);
-            if (k0 >= warp_keys || k0 + kTileN <= warp_first) continue;   // nothing for this warp's rows in this tile (it keeps the barriers)
+            if (k0 >= warp_keys || (BLOCKS && k0 + kTileN <= warp_first)) continue;   // nothing for this warp's rows in this tile (it keeps the barriers)
             const bf* Kb = Ks + buf * kTileN * RS;
             const bf* Vb = Vs + buf * kTileN * RSV;
             float s[kTileN / 8][4];
@@ -526,7 +527,7 @@ __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = k0 + nt * 8 + tig * 2 + (e & 1);
-                    const float v = (j <= ((e & 2) ? p_hi : p_lo) && j >= ((e & 2) ? f_hi : f_lo)) ? s[nt][e] : -INFINITY;
+                    const float v = (j <= ((e & 2) ? p_hi : p_lo) && (!BLOCKS || j >= ((e & 2) ? f_hi : f_lo))) ? s[nt][e] : -INFINITY;
                     s[nt][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -598,9 +599,18 @@ static int launch_tile(const PA& a, cudaStream_t s) {
     static_assert(kTileM == kTileN, "the Q tile borrows a K buffer");
     constexpr int smem = 2 * kTileN * (D + 8) * 2 + 2 * kTileN * (DV + 8) * 2 + 2 * kTileM * 4;
     static unsigned long long done = 0;
-    const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D, DV>, smem, done);
+    static_assert(DV % D == 0, "a thread brings DV / D value chunks with every key chunk");
+    const dim3 grid((a.n_tokens + kTileM - 1) / kTileM, a.heads * a.maps);
+    if (a.chunk > 0) {
+        static unsigned long long done_b = 0;
+        const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D, DV, true>, smem, done_b);
+        if (e != cudaSuccess) return (int)e;
+        paged_attn_tile_kernel<D, DV, true><<<grid, 128, smem, s>>>(a);
+        return (int)cudaGetLastError();
+    }
+    const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D, DV, false>, smem, done);
     if (e != cudaSuccess) return (int)e;
-    paged_attn_tile_kernel<D, DV><<<dim3((a.n_tokens + kTileM - 1) / kTileM, a.heads * a.maps), 128, smem, s>>>(a);
+    paged_attn_tile_kernel<D, DV, false><<<grid, 128, smem, s>>>(a);
     return (int)cudaGetLastError();
 }
 // the (dim, vdim) pairs the tile kernel is built for: equal sizes, and values twice as wide as the keys

@@ -36,6 +36,10 @@ __device__ __forceinline__ void gg_store(const GG& g, TC* C, long long row, int 
     else if (g.epi == B200_GG_GLU) v = v / (1.f + expf(-v)) * v2;
     else if (g.epi == B200_GG_GLU_GELU) v = gelu_tanh_f(v) * v2;
     else if (g.epi == B200_GG_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+    else if (g.epi == B200_GG_BIAS_SOFTPLUS) {
+        v += g.aux[aux_off + row * g.ld_aux + col];
+        v = v > 20.f ? v : log1pf(expf(v));
+    }
     C[row * g.ldc + col] = DT<TC>::from_f(v);
 }
 
@@ -379,7 +383,7 @@ using namespace b200;
 extern "C" int b200_gemm_grouped(const b200_gemm_grouped_args* p, void* stream) {
     if (!p || !p->A || !p->W || !p->C || p->N <= 0 || p->K <= 0 || p->M < 0 || p->batch < 1) return B200_EINVAL;
     if (p->M == 0) return B200_OK;
-    if (p->epi == B200_GG_SIGMOID_MUL && !p->aux) return B200_EINVAL;
+    if ((p->epi == B200_GG_SIGMOID_MUL || p->epi == B200_GG_BIAS_SOFTPLUS) && !p->aux) return B200_EINVAL;
     GG g;
     g.A = p->A; g.W = p->W; g.C = p->C; g.aux = p->aux; g.a_rows = p->a_rows; g.group_off = p->group_off;
     g.lda = p->lda; g.ldw = p->ldw; g.ldc = p->ldc; g.ld_aux = p->ld_aux;

@@ -57,6 +57,7 @@ struct Scan {
     int channels, n_state;
     // chunk form (entries of at least chunk_from tokens): chunk u covers tokens [chunk_first[u], + chunk) of entry chunk_ent[u]
     int chunk, chunk_from; const int* chunk_ent; const int* chunk_first; float* summary;
+    int dt_ready;   // dt_raw holds the step sizes themselves
 };
 
 constexpr int kScanThreads = 128, kScanPerLane = 8, kScanGroup = 4;
@@ -72,6 +73,9 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 template <typename T, int LP, int MODE>
 __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan a) {
     constexpr int CPB = kScanThreads / LP;   // channels per CTA
+    // bfloat16 serving: exp(dt A) as 2^(dt A log2 e) on the special-function unit (relative error about 2^-22); fp32
+    // serving keeps the accurate exponential
+    constexpr bool kFast = sizeof(T) == 2;
     const int lane = threadIdx.x % LP, c = blockIdx.x * CPB + threadIdx.x / LP, N = a.n_state, Cn = a.channels;
     const bool live = c < Cn;
     const int cc = live ? c : Cn - 1;        // lanes beyond the last channel walk along (shuffles need them) and store nothing
@@ -100,7 +104,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
 #pragma unroll
     for (int k = 0; k < kScanPerLane; ++k) {
         const int n = lane + k * LP;
-        Av[k] = n < N ? a.A[(size_t)cc * N + n] : 0.f;
+        Av[k] = n < N ? a.A[(size_t)cc * N + n] * (kFast ? 1.4426950408889634f : 1.f) : 0.f;
         if (MODE == 0) S[k] = (n < N && first_pos > 0) ? st[n] : 0.f;
         else if (MODE == 1) S[k] = 0.f;
         else S[k] = n < N ? sm[1 + n] : 0.f;
@@ -128,12 +132,12 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
 #pragma unroll
         for (int j = 0; j < kScanGroup; ++j) {
             if (i0 + j >= len) break;
-            const float dt = softplus_f(dtr[j] + dtb), dx = dt * xv[j];
+            const float dt = a.dt_ready ? dtr[j] : softplus_f(dtr[j] + dtb), dx = dt * xv[j];
             float y = 0.f;
 #pragma unroll
             for (int k = 0; k < kScanPerLane; ++k) {
                 if (lane + k * LP < N) {
-                    S[k] = fmaf(expf(dt * Av[k]), S[k], dx * Bv[j][k]);
+                    S[k] = fmaf(kFast ? exp2f(dt * Av[k]) : expf(dt * Av[k]), S[k], dx * Bv[j][k]);
                     if (MODE != 1) y = fmaf(S[k], Cv[j][k], y);
                 }
             }
@@ -273,7 +277,7 @@ extern "C" int b200_selective_scan(const b200_selective_scan_args* p, void* stre
     if (p->n_entries == 0 || p->n_tokens == 0) return B200_OK;
     if (p->n_entries > 65535) return B200_EUNSUPPORTED;
     Scan a{p->x, p->dt_raw, p->dt_bias, p->B, p->C, p->ld_bc, p->z, p->ld_z, p->A, p->D, p->state, p->out,
-           p->ent_row, p->ent_len, p->slot, p->pos, p->channels, p->n_state, 0, 0, nullptr, nullptr, nullptr};
+           p->ent_row, p->ent_len, p->slot, p->pos, p->channels, p->n_state, 0, 0, nullptr, nullptr, nullptr, p->dt_ready};
     const int lp = scan_lanes(p->n_state);
     cudaStream_t s = (cudaStream_t)stream;
     // long entries: chunk-local scans in parallel, a walk over the chunk summaries, then every chunk again from its true start

@@ -643,16 +643,17 @@ int Tomalix::enqueue(int T, int W, int longest_entry, int longest_context, bool 
                 TX_OP(b200_conv_state_update(u, L.n_in, R.ring.data(), seq_.d_slot(), seq_.d_pos(), seq_.d_end(), T, sc.inner, sc.taps, stream_));
             const int nbc = sc.dt_rank + 2 * sc.state;
             TX_OP(gemm(xc_, sc.w_x, bc_, B200_F32, T, nbc, sc.inner));
-            {   // dt_raw = bc[:, 0:dt_rank] W_dt^T: the fp32 columns are the operand as they are (leading dimension nbc)
+            {   // dt = softplus(bc[:, 0:dt_rank] W_dt^T + bias): the fp32 columns are the operand as they are (leading dimension nbc)
                 b200_gemm_grouped_args g{};
                 g.A = bc_; g.lda = nbc; g.W = sc.w_dt; g.ldw = sc.dt_rank; g.trans_b = 1;
+                g.epi = B200_GG_BIAS_SOFTPLUS; g.aux = sc.dt_b; g.ld_aux = 0;   // the step sizes leave the GEMM finished
                 g.C = dtr_; g.ldc = sc.inner;
                 g.M = T; g.N = sc.inner; g.K = sc.dt_rank; g.batch = 1;
                 g.a_dtype = B200_F32; g.w_dtype = dt; g.c_dtype = B200_F32;
                 TX_OP(b200_gemm_grouped(&g, stream_));
             }
             b200_selective_scan_args sa{};
-            sa.x = xc32_; sa.dt_raw = dtr_; sa.dt_bias = sc.dt_b;
+            sa.x = xc32_; sa.dt_raw = dtr_; sa.dt_ready = 1;
             sa.B = bc_ + sc.dt_rank; sa.C = bc_ + sc.dt_rank + sc.state; sa.ld_bc = nbc;
             sa.z = u + sc.inner; sa.ld_z = L.n_in;
             sa.A = sc.A; sa.D = sc.Dv;

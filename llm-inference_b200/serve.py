@@ -8,7 +8,7 @@ import numpy as np
 from . import capi
 
 F32, BF16 = 0, 2
-GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU, GG_RELU2 = 0, 1, 2, 3, 4
+GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU, GG_RELU2, GG_BIAS_SOFTPLUS = 0, 1, 2, 3, 4, 5
 ROPE_HALF, ROPE_INTERLEAVED = 0, 1
 _vp, _i, _f, _sz, _ll = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_longlong
 
@@ -61,7 +61,7 @@ class SelectiveScanArgs(C.Structure):
                 ("A", _vp), ("D", _vp), ("state", _vp), ("out", _vp), ("out_dtype", _i),
                 ("ent_row", _vp), ("ent_len", _vp), ("slot", _vp), ("pos", _vp),
                 ("n_entries", _i), ("n_tokens", _i), ("channels", _i), ("n_state", _i), ("longest_entry", _i),
-                ("workspace", _vp), ("workspace_bytes", _sz)]
+                ("workspace", _vp), ("workspace_bytes", _sz), ("dt_ready", _i)]
 
 
 class RetentionArgs(C.Structure):
