@@ -19,7 +19,7 @@ def S(pkg):
 
 def test_registry_lists_the_families(S):
     fams = S.lib().b200_model_families().decode().split(",")
-    assert "Nekodra" in fams and "Musilorn" in fams and "llama" in fams
+    assert "Nekodra" in fams and "Musilorn" in fams and "Tomalix" in fams and "llama" in fams
 
 
 def test_unknown_architecture_and_broken_config(S, tmp_path):
@@ -44,6 +44,81 @@ def test_musilorn_configuration_errors_end_before_any_cuda_call(S, tmp_path):
                                           '"layers": [{"type": "attention", "mixer": {}, "mlp": null}]}')
     with pytest.raises(RuntimeError, match="residual_mult"):
         S.Model(tmp_path)
+
+
+def test_tomalix_configuration_errors_end_before_any_cuda_call(S, tmp_path):
+    head = '{"architecture": "Tomalix", "width": 8, "vocab": 5, "norm": {"eps": 1e-5}, '
+    (tmp_path / "config.json").write_text(head + '"layers": []}')
+    with pytest.raises(RuntimeError, match="required"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "retention", "mixer": {}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="not part of this family"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "attention_2", "mixer": {}, "mlp": {"kind": "glu"}}]}')
+    with pytest.raises(RuntimeError, match="feed-forward kind"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"loop": {"start": 0, "stop": 2, "times": 2}, '
+                                          '"layers": [{"type": "attention_2", "mixer": {}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="loop"):
+        S.Model(tmp_path)
+
+
+def test_tomalix_oracle_pieces_agree_with_closed_forms():
+    """the plain implementation of the third family: the offset norm, the three frequency rules, the rotation, the block
+    mask, the two-map combination, the convolution, the scan against its unrolled sum, the router, the order of layer runs"""
+    import tomalix_oracle as T
+    g = torch.Generator().manual_seed(2)
+    D = torch.float64
+    x = torch.randn(4, 6, generator=g, dtype=D)
+    assert torch.allclose(T.rms_norm(x, torch.zeros(6, dtype=D), 0.0), x / x.pow(2).mean(-1, keepdim=True).sqrt())
+    assert torch.allclose(T.rms_norm(x, torch.full((6,), 0.5, dtype=D), 0.0), 1.5 * T.unit_rms(x, 0.0))
+    rot = dict(base=100.0, dims=8)
+    plain, amp0 = T.rot_frequencies(rot, "plain")
+    lin, amp1 = T.rot_frequencies(dict(rot, scaling=dict(factor=4.0)), "linear")
+    assert amp0 == 1.0 and amp1 == 1.0 and torch.allclose(lin, plain / 4) and float(plain[1]) == pytest.approx(100.0 ** (-2 / 8))
+    # the ramp: index where `fast` turns fit into `original` positions -> kept; beyond the index of `slow` -> divided by factor
+    sc = dict(factor=2.0, original=64, fast=4.0, slow=0.5)
+    ramp, amp = T.rot_frequencies(dict(rot, scaling=sc), "ramp")
+    idx = lambda turns: 8 * math.log(64 / (2 * math.pi * turns)) / (2 * math.log(100.0))
+    lo, hi = max(math.floor(idx(4.0)), 0), min(math.ceil(idx(0.5)), 7)
+    assert (lo, hi) == (0, 3) and amp == pytest.approx(0.1 * math.log(2.0) + 1)
+    assert ramp[0] == plain[0] and torch.allclose(ramp[3], plain[3] / 2) and torch.allclose(ramp[1], plain[1] * (1 - 1 / 3) + plain[1] / 2 / 3)
+    q = torch.randn(5, 2, 8, generator=g, dtype=D)
+    r = T.rotate_half(q, dict(base=100.0, dims=4), "plain")
+    a = 3 * 100.0 ** (-2 / 4)
+    assert torch.equal(r[..., 4:], q[..., 4:]) and torch.equal(r[0], q[0])
+    assert torch.allclose(r[3, 1, 1], q[3, 1, 1] * math.cos(a) - q[3, 1, 3] * math.sin(a))
+    assert torch.allclose(r[3, 1, 3], q[3, 1, 3] * math.cos(a) + q[3, 1, 1] * math.sin(a))
+    m = T.visible(7, 3)
+    assert m[5].tolist() == [False, False, False, True, True, True, False] and m[6].tolist() == [False] * 6 + [True]
+    assert T.visible(3).tolist() == [[True, False, False], [True, True, False], [True, True, True]]
+    u, w, b = torch.randn(6, 3, generator=g, dtype=D), torch.randn(3, 4, generator=g, dtype=D), torch.randn(3, generator=g, dtype=D)
+    y = T.causal_conv(u, w, b)
+    assert torch.allclose(y[0], b + w[:, 3] * u[0]) and torch.allclose(y[5], b + (w.T * u[2:6]).sum(0))
+    # the scan of one channel and one state is a weighted sum over the past
+    W = {"in": torch.tensor([[1.0], [0.5]], dtype=D), "conv": torch.ones(1, 1, dtype=D),
+         "conv.b": torch.zeros(1, dtype=D), "x": torch.tensor([[0.3], [1.0], [2.0]], dtype=D), "dt": torch.ones(1, 1, dtype=D),
+         "dt.b": torch.zeros(1, dtype=D), "A_log": torch.zeros(1, 1, dtype=D), "D": torch.tensor([0.25], dtype=D), "o": torch.ones(1, 1, dtype=D)}
+    h = torch.randn(4, 1, generator=g, dtype=D)
+    got = T.selective_scan(h, dict(inner=1, state=1, dt_rank=1, conv=1), W, "")
+    xs, z = T.silu(h[:, 0]), 0.5 * h[:, 0]
+    dt = torch.log1p(torch.exp(0.3 * xs))
+    want = []
+    for t in range(4):
+        acc = sum(math.exp(-float(dt[j + 1: t + 1].sum())) * float(dt[j] * xs[j]) * float(xs[j]) for j in range(t + 1))
+        want.append((acc * 2.0 * float(xs[t]) + 0.25 * float(xs[t])) * float(T.silu(z[t])))
+    assert torch.allclose(got[:, 0], torch.tensor(want, dtype=D))
+    # router: the two largest biased logits, weights over those two alone
+    Wr = {"router": torch.eye(3, dtype=D), "router.b": torch.tensor([0.0, 0.0, -2.0], dtype=D)}
+    for e in range(3):
+        Wr["e%d.up" % e], Wr["e%d.down" % e] = torch.full((1, 3), float(e + 1), dtype=D), torch.ones(3, 1, dtype=D)
+    hh = torch.tensor([[2.0, 1.0, -1.0]], dtype=D)                     # logits 2, 1, -3: experts 0 and 1
+    out = T.routed_ff(hh, dict(router=dict(experts=3, top=2)), Wr, "")
+    p = torch.softmax(torch.tensor([2.0, 1.0], dtype=D), 0)
+    assert torch.allclose(out[0], (p[0] * 2.0 ** 2 + p[1] * 4.0 ** 2).expand(3))
+    cfg = dict(layers=[0, 1, 2, 3], loop=dict(start=1, stop=3, times=2))
+    assert T.layer_order(cfg) == [(0, None), (1, 0), (2, None), (1, 1), (2, None), (3, None)]
+    assert T.layer_order(dict(layers=[0, 1])) == [(0, None), (1, None)]
 
 
 def test_musilorn_oracle_pieces_agree_with_closed_forms():
