@@ -70,7 +70,10 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 //         chunk of an entry has no successor and is skipped).
 // MODE 2: one chunk from the state that the chunk scan left at its start (summary holds it), with outputs; the last
 //         chunk of an entry stores the slot's state.
-template <typename T, int LP, int MODE>
+// FULL: every lane owns eight consecutive states (n_state == 8 LP) and the B / C rows allow 16-byte loads: no predicates on
+// the state count, two vector loads per operand and token. Otherwise state n of lane l is l + k LP and every access is
+// predicated.
+template <typename T, int LP, int MODE, bool FULL>
 __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan a) {
     constexpr int CPB = kScanThreads / LP;   // channels per CTA
     // bfloat16 serving: exp(dt A) as 2^(dt A log2 e) on the special-function unit (relative error about 2^-22); fp32
@@ -103,7 +106,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
     float* sm = MODE == 0 ? nullptr : a.summary + ((size_t)unit * Cn + cc) * (N + 1);
 #pragma unroll
     for (int k = 0; k < kScanPerLane; ++k) {
-        const int n = lane + k * LP;
+        const int n = FULL ? lane * kScanPerLane + k : lane + k * LP;
         Av[k] = n < N ? a.A[(size_t)cc * N + n] * (kFast ? 1.4426950408889634f : 1.f) : 0.f;
         if (MODE == 0) S[k] = (n < N && first_pos > 0) ? st[n] : 0.f;
         else if (MODE == 1) S[k] = 0.f;
@@ -122,11 +125,22 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
             dtr[j] = in ? __ldg(a.dt_raw + t * Cn + cc) : 0.f;
             xv[j] = in ? __ldg(a.x + t * Cn + cc) : 0.f;
             zv[j] = (MODE != 1 && in && lane == 0) ? __ldg(a.z + t * a.ld_z + cc) : 0.f;
+            if (FULL) {
+                const float4* bp = reinterpret_cast<const float4*>(a.B + t * a.ld_bc + lane * kScanPerLane);
+                const float4* cp = reinterpret_cast<const float4*>(a.C + t * a.ld_bc + lane * kScanPerLane);
 #pragma unroll
-            for (int k = 0; k < kScanPerLane; ++k) {
-                const int n = lane + k * LP;
-                Bv[j][k] = (in && n < N) ? __ldg(a.B + t * a.ld_bc + n) : 0.f;
-                Cv[j][k] = (MODE != 1 && in && n < N) ? __ldg(a.C + t * a.ld_bc + n) : 0.f;
+                for (int h = 0; h < kScanPerLane / 4; ++h) {
+                    const float4 b4 = __ldg(bp + h), c4 = MODE != 1 ? __ldg(cp + h) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    Bv[j][4 * h] = b4.x; Bv[j][4 * h + 1] = b4.y; Bv[j][4 * h + 2] = b4.z; Bv[j][4 * h + 3] = b4.w;
+                    Cv[j][4 * h] = c4.x; Cv[j][4 * h + 1] = c4.y; Cv[j][4 * h + 2] = c4.z; Cv[j][4 * h + 3] = c4.w;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < kScanPerLane; ++k) {
+                    const int n = lane + k * LP;
+                    Bv[j][k] = (in && n < N) ? __ldg(a.B + t * a.ld_bc + n) : 0.f;
+                    Cv[j][k] = (MODE != 1 && in && n < N) ? __ldg(a.C + t * a.ld_bc + n) : 0.f;
+                }
             }
         }
 #pragma unroll
@@ -136,7 +150,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
             float y = 0.f;
 #pragma unroll
             for (int k = 0; k < kScanPerLane; ++k) {
-                if (lane + k * LP < N) {
+                if (FULL || lane + k * LP < N) {
                     S[k] = fmaf(kFast ? exp2f(dt * Av[k]) : expf(dt * Av[k]), S[k], dx * Bv[j][k]);
                     if (MODE != 1) y = fmaf(S[k], Cv[j][k], y);
                 }
@@ -153,13 +167,13 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(const Scan
         if (lane == 0) sm[0] = dt_sum;
 #pragma unroll
         for (int k = 0; k < kScanPerLane; ++k) {
-            const int n = lane + k * LP;
+            const int n = FULL ? lane * kScanPerLane + k : lane + k * LP;
             if (n < N) sm[1 + n] = S[k];
         }
     } else if (last_chunk) {
 #pragma unroll
         for (int k = 0; k < kScanPerLane; ++k) {
-            const int n = lane + k * LP;
+            const int n = FULL ? lane * kScanPerLane + k : lane + k * LP;
             if (n < N) st[n] = S[k];
         }
     }
@@ -223,18 +237,25 @@ static int scan_lanes(int n_state) {
     while (lp < 32 && lp * kScanPerLane < n_state) lp *= 2;
     return lp;
 }
+template <typename T, int MODE, bool FULL>
+static void scan_dispatch_lp(const Scan& a, int lp, dim3 grid, cudaStream_t s) {
+    switch (lp) {
+        case 1: selective_scan_kernel<T, 1, MODE, FULL><<<grid, kScanThreads, 0, s>>>(a); break;
+        case 2: selective_scan_kernel<T, 2, MODE, FULL><<<grid, kScanThreads, 0, s>>>(a); break;
+        case 4: selective_scan_kernel<T, 4, MODE, FULL><<<grid, kScanThreads, 0, s>>>(a); break;
+        case 8: selective_scan_kernel<T, 8, MODE, FULL><<<grid, kScanThreads, 0, s>>>(a); break;
+        case 16: selective_scan_kernel<T, 16, MODE, FULL><<<grid, kScanThreads, 0, s>>>(a); break;
+        default: selective_scan_kernel<T, 32, MODE, FULL><<<grid, kScanThreads, 0, s>>>(a); break;
+    }
+}
 template <typename T, int MODE>
 static void scan_dispatch(const Scan& a, int lp, int units, cudaStream_t s) {
     const unsigned gx = (unsigned)((a.channels + kScanThreads / lp - 1) / (kScanThreads / lp));
     const dim3 grid(gx, units);
-    switch (lp) {
-        case 1: selective_scan_kernel<T, 1, MODE><<<grid, kScanThreads, 0, s>>>(a); break;
-        case 2: selective_scan_kernel<T, 2, MODE><<<grid, kScanThreads, 0, s>>>(a); break;
-        case 4: selective_scan_kernel<T, 4, MODE><<<grid, kScanThreads, 0, s>>>(a); break;
-        case 8: selective_scan_kernel<T, 8, MODE><<<grid, kScanThreads, 0, s>>>(a); break;
-        case 16: selective_scan_kernel<T, 16, MODE><<<grid, kScanThreads, 0, s>>>(a); break;
-        default: selective_scan_kernel<T, 32, MODE><<<grid, kScanThreads, 0, s>>>(a); break;
-    }
+    const bool full = a.n_state == lp * kScanPerLane && a.ld_bc % 4 == 0 && (reinterpret_cast<uintptr_t>(a.B) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(a.C) & 15u) == 0;
+    if (full) scan_dispatch_lp<T, MODE, true>(a, lp, grid, s);
+    else scan_dispatch_lp<T, MODE, false>(a, lp, grid, s);
     count_launch();
 }
 }  // namespace b200

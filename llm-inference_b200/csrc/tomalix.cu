@@ -141,7 +141,7 @@ private:
         owned_.push_back(p);
         return p;
     }
-    int parse_attn(const Json& mx, const std::string& where, int maps, TxAttn& at, std::string& err);
+    int parse_attn(const Json& mx, const std::string& where, int maps, bool ramp_allowed, TxAttn& at, std::string& err);
     int gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi = B200_GG_NONE);
     int ensure_scratch(int T, int W);
     int enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err);
@@ -199,10 +199,11 @@ private:
     } while (0)
 
 // Sizes, scale and rotary frequencies of one attention. f_i = base^(-2i/dims); "scaling" {factor} divides every f_i by
-// factor; "scaling" {factor, original, fast, slow} blends f_i / factor and f_i with a ramp over the index i between the
-// indices whose wavelengths make `fast` and `slow` turns within `original` positions, and multiplies cos and sin by
-// 0.1 ln(factor) + 1. Equal (frequencies, amplitude) share one cos / sin table per step.
-int Tomalix::parse_attn(const Json& mx, const std::string& where, int maps, TxAttn& at, std::string& err) {
+// factor; "scaling" {factor, original, fast, slow} (where the mixer has the ramped rule: ramp_allowed) blends f_i / factor
+// and f_i with a ramp over the index i between the indices whose wavelengths make `fast` and `slow` turns within
+// `original` positions, and multiplies cos and sin by 0.1 ln(factor) + 1. Equal (frequencies, amplitude) share one cos /
+// sin table per step.
+int Tomalix::parse_attn(const Json& mx, const std::string& where, int maps, bool ramp_allowed, TxAttn& at, std::string& err) {
     at.heads = (int)mx.integer("heads", 0);
     at.kv_heads = (int)mx.integer("kv_heads", at.heads);
     at.dim = (int)mx.integer("dim", 0);
@@ -229,7 +230,7 @@ int Tomalix::parse_attn(const Json& mx, const std::string& where, int maps, TxAt
     if (sc && !sc->is_null()) {
         const double factor = sc->number("factor", 1.0);
         if (!(factor > 0.0)) { err = where + "rot.scaling.factor must be positive"; return B200_EINVAL; }
-        if (sc->has("original")) {
+        if (ramp_allowed && sc->has("original")) {
             const double orig = sc->number("original", 0.0), fast = sc->number("fast", 32.0), slow = sc->number("slow", 1.0);
             if (!(orig > 0.0) || !(fast > 0.0) || !(slow > 0.0)) { err = where + "rot.scaling needs positive original, fast, slow"; return B200_EINVAL; }
             auto index_of = [&](double turns) { return d * std::log(orig / (2.0 * kPi * turns)) / (2.0 * std::log(base)); };
@@ -362,7 +363,7 @@ int Tomalix::load(const ModelDir& dir, const b200_model_options& opt, std::strin
             if (!left || left->is_null() || !right || right->is_null()) { err = where + "a parallel mixer needs left and right"; return B200_EINVAL; }
             L.left_scale = (float)mx.number("left_scale", 1.0);
             L.right_scale = (float)mx.number("right_scale", 1.0);
-            TX_TRY(parse_attn(*left, where, 1, L.at, err));
+            TX_TRY(parse_attn(*left, where, 1, true, L.at, err));
             TxAttn& at = L.at;
             at.q_off = 0; at.k_off = at.nq(); at.v_off = at.k_off + at.nk(); at.g_off = at.v_off + at.nv();
             TxScan& sc = L.sc;
@@ -400,7 +401,7 @@ int Tomalix::load(const ModelDir& dir, const b200_model_options& opt, std::strin
         } else {
             const bool diff = type == "attention";
             L.kind = diff ? kMixDiff : kMixPlain;
-            TX_TRY(parse_attn(mx, where, diff ? 2 : 1, L.at, err));
+            TX_TRY(parse_attn(mx, where, diff ? 2 : 1, !diff, L.at, err));
             TxAttn& at = L.at;
             at.q_off = 0; at.k_off = at.nq(); at.v_off = at.k_off + at.nk();
             L.n_in = at.v_off + at.nv();

@@ -159,7 +159,8 @@ def plain_maps(q, k, v, pos, heads, kv, maps, scale, chunk):
 
 @pytest.mark.parametrize("kind", ["f32", "bf16"])
 @pytest.mark.parametrize("heads,kv,dim,vdim,chunk,maps", [(4, 2, 16, 8, 7, 1), (6, 1, 64, 64, 40, 1), (3, 3, 10, 6, 0, 2), (2, 1, 32, 64, 0, 2),
-                                                          (8, 2, 64, 128, 16, 1), (4, 1, 128, 128, 100, 2), (2, 2, 48, 48, 0, 1)])
+                                                          (8, 2, 64, 128, 16, 1), (4, 1, 128, 128, 100, 2), (2, 2, 48, 48, 0, 1),
+                                                          (2, 1, 128, 256, 0, 2), (4, 4, 128, 256, 50, 1), (2, 2, 32, 32, 5, 1), (4, 2, 32, 64, 33, 2)])
 def test_paged_attention_with_blocks_and_maps(S, kind, heads, kv, dim, vdim, chunk, maps):
     code, g = code_of(S, kind), gen(heads * dim + chunk)
     PR, scale = 16, 1.7 / math.sqrt(dim)
@@ -304,17 +305,19 @@ def plain_scan(x, dt_raw, dt_b, B, Cm, z, A, D):
     return torch.stack(out), S_
 
 
-@pytest.mark.parametrize("Cn,N", [(37, 1), (20, 5), (64, 16), (9, 70), (130, 32)])
+@pytest.mark.parametrize("Cn,N", [(37, 1), (20, 5), (64, 16), (9, 70), (130, 32), (33, 8), (12, 256), (5, 24)])
 def test_selective_scan_in_portions_with_a_carried_state(S, Cn, N):
-    """two sequences; portions of one, two and hundreds of tokens (the chunk form); a stale state in both slots"""
+    """two sequences; portions of one, two and hundreds of tokens (the chunk form); a stale state in both slots. State counts
+    of 8 per lane with 16-byte aligned B / C rows take the vector-load form of the kernel, the others the predicated one"""
     g = gen(Cn + N)
     lens = {0: 700, 1: 90}
-    ld_bc, ld_z = 2 * N + 3, Cn + 2
+    off = 4 if N % 8 == 0 else 1                      # first B column in the [.. | B | C | ..] rows
+    ld_bc, ld_z = 2 * N + off + (4 - off % 4) % 4 + (0 if N % 8 == 0 else 2), Cn + 2
     mk = lambda n, c, s=1.0: torch.randn(n, c, generator=g) * s
     x, dtr, bc, z = ({b: mk(n, c, s) for b, n in lens.items()} for c, s in ((Cn, 1.0), (Cn, 1.0), (ld_bc, 1.0), (ld_z, 1.0)))
     A = -torch.exp(torch.randn(Cn, N, generator=g) * 0.5)
     D, dtb = torch.randn(Cn, generator=g), torch.randn(Cn, generator=g) * 0.5 - 1.5
-    want = {b: plain_scan(x[b].double(), dtr[b].double(), dtb.double(), bc[b][:, 1: 1 + N].double(), bc[b][:, 1 + N: 1 + 2 * N].double(),
+    want = {b: plain_scan(x[b].double(), dtr[b].double(), dtb.double(), bc[b][:, off: off + N].double(), bc[b][:, off + N: off + 2 * N].double(),
                           z[b][:, 2:].double(), A.double(), D.double()) for b in lens}
     state = dev(torch.full((3, Cn, N), 9.0))
     plan = [[(1, 1), (0, 2)], [(0, 1)], [(0, 1), (1, 2)], [(0, 600), (1, 80)], [(1, 7), (0, 96)]]
@@ -333,7 +336,7 @@ def test_selective_scan_in_portions_with_a_carried_state(S, Cn, N):
         out = torch.zeros(T, Cn, device="cuda")
         need = S.lib().b200_selective_scan_workspace_bytes(T, len(step), Cn, N)
         ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
-        a = S.SelectiveScanArgs(dx.data_ptr(), ddt.data_ptr(), dev(dtb).data_ptr(), dbc.data_ptr() + 4, dbc.data_ptr() + 4 * (1 + N), ld_bc,
+        a = S.SelectiveScanArgs(dx.data_ptr(), ddt.data_ptr(), dev(dtb).data_ptr(), dbc.data_ptr() + 4 * off, dbc.data_ptr() + 4 * (off + N), ld_bc,
                                 dz.data_ptr() + 8, ld_z, dev(A).data_ptr(), dev(D).data_ptr(), state.data_ptr(), out.data_ptr(), S.F32,
                                 ints(ent_row).data_ptr(), ints([c for _, c in step]).data_ptr(), slot.data_ptr(), pos.data_ptr(),
                                 len(step), T, Cn, N, max(c for _, c in step), ws.data_ptr(), need)
