@@ -4,10 +4,13 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <deque>
 #include <map>
 
 #include "common.cuh"
+#include "launch_count.h"
 
 namespace b200 {
 
@@ -128,6 +131,177 @@ int SequenceBatch::release(int slot) {
     if (slot < 0 || slot >= n_slots) return B200_EINVAL;
     pool.release(slot);
     length[slot] = 0;
+    return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// StepRunner
+// ------------------------------------------------------------------------------------------
+StepRunner::~StepRunner() {
+    if (stream_) cudaStreamSynchronize(stream_);
+    drop_graphs();
+    for (void* p : owned_) cudaFree(p);
+    cudaFree(ws_);
+    cudaFree(attn_ws_);
+    cudaFree(capture_);
+    if (logits_host_) cudaFreeHost(logits_host_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+int StepRunner::init_runner(std::string& err) {
+    if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) { err = "no CUDA device: this library has no CPU path"; return B200_EINVAL; }
+    const char* e = getenv("B200_NO_GRAPH");
+    graphs_enabled_ = !(e && e[0] == '1');
+    return B200_OK;
+}
+
+void* StepRunner::dalloc(size_t bytes) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) return nullptr;
+    owned_.push_back(p);
+    return p;
+}
+
+void StepRunner::drop_graphs() {
+    for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);
+    graphs_.clear();
+}
+
+int StepRunner::slot_pages(int slot, int* out, int max_n) const {
+    const int n = std::min(max_n, seq_.pool.owned(slot));
+    for (int i = 0; i < n; ++i) out[i] = seq_.pool.list(slot)[i];
+    return n;
+}
+
+int StepRunner::release(int slot) {
+    cudaStreamSynchronize(stream_);   // pages and state change owner only behind the work that reads them
+    return seq_.release(slot);
+}
+
+int StepRunner::captured_layers(float* out, size_t max_floats) {
+    const size_t n = (size_t)layer_count() * captured_tokens_ * D_;
+    if (!capture_ || n == 0) return 0;
+    if (n > max_floats) return B200_EWORKSPACE;
+    cudaStreamSynchronize(stream_);
+    if (cudaMemcpy(out, capture_, n * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) return B200_EINVAL;
+    return captured_tokens_;
+}
+
+void StepRunner::keep_layer(size_t run, const float* x, int T) {
+    if (capture_on_) cudaMemcpyAsync(capture_ + run * (size_t)T * D_, x, (size_t)T * D_ * 4, cudaMemcpyDeviceToDevice, stream_);
+}
+
+int StepRunner::ensure_logits_host(int W) {
+    const size_t lf = (size_t)W * vocab_;
+    if (lf <= logits_host_floats_) return B200_OK;
+    if (logits_host_) cudaFreeHost(logits_host_);
+    logits_host_ = nullptr;
+    logits_host_floats_ = 0;
+    if (cudaMallocHost(&logits_host_, lf * 4) != cudaSuccess) return B200_ENOMEM;
+    logits_host_floats_ = lf;
+    return B200_OK;
+}
+
+int StepRunner::gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi) {
+    const size_t need = b200_linear_ex_workspace_bytes(M, N, K);
+    if (need > ws_bytes_ && !capturing_) {
+        cudaStreamSynchronize(stream_);
+        ++buffers_epoch_;
+        cudaFree(ws_);
+        ws_ = nullptr;
+        ws_bytes_ = 0;
+        if (cudaMalloc(&ws_, need) == cudaSuccess) ws_bytes_ = need;   // without it the call runs with a single split
+    }
+    return b200_linear_ex(A, W, C, M, N, K, dtype_, c_dt, epi, ws_, ws_bytes_, stream_);
+}
+
+int StepRunner::step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) {
+    if (entries.empty()) return B200_OK;
+    const uint64_t launches0 = b200_launch_count();
+    int rc = seq_.begin_step(entries, stream_, err);
+    if (rc != B200_OK) return rc;
+    const int T = seq_.n_tokens, W = seq_.n_want, D = D_;
+    if (ensure_scratch(T, std::max(W, 1)) != B200_OK) { err = "step: out of device memory for the scratch buffers"; return B200_ENOMEM; }
+    int longest_entry = 0, longest_context = 0;
+    for (const StepEntry& en : entries) {
+        longest_entry = std::max(longest_entry, en.n_tokens);
+        longest_context = std::max(longest_context, seq_.length[en.slot]);
+    }
+    {   // room for the shares of split contexts (batches of few rows) and for the chunk states of long recurrent entries
+        const size_t need = step_workspace_bytes(T, seq_.n_entries);
+        if (need > attn_ws_bytes_) {
+            cudaStreamSynchronize(stream_);
+            ++buffers_epoch_;
+            cudaFree(attn_ws_);
+            attn_ws_ = nullptr;
+            attn_ws_bytes_ = 0;
+            if (cudaMalloc(&attn_ws_, need) == cudaSuccess) attn_ws_bytes_ = need;
+        }
+    }
+    if (capture_on_) {
+        const size_t need = (size_t)layer_count() * T * D;
+        if (capture_cap_ < need) {
+            cudaStreamSynchronize(stream_);
+            cudaFree(capture_);
+            capture_ = nullptr;
+            capture_cap_ = 0;
+            if (cudaMalloc(&capture_, need * 4) != cudaSuccess) { err = "step: no memory to keep the layers"; return B200_ENOMEM; }
+            capture_cap_ = need;
+        }
+        captured_tokens_ = T;
+    }
+    // Batches of single tokens repeat their shape step after step: the second time a shape is seen its launch sequence is
+    // captured into a CUDA graph, from then on the step is one graph launch (the per-step tables are read through fixed
+    // pointers that begin_step refreshes). Anything that moves a buffer drops the graphs.
+    const bool want_ids = ids_out != nullptr;
+    if (buffers_epoch_ != graph_epoch_ || seq_.d_ids() != graph_tables_) {   // a buffer was reallocated (even to the same address:
+        drop_graphs();                                                         // the carving inside it changed)
+        graph_epoch_ = buffers_epoch_;
+        graph_tables_ = seq_.d_ids();
+    }
+    const bool graph_ok = graphs_enabled_ && longest_entry == 1 && !capture_on_ && T <= 4096 && W <= 4096;
+    const int ctx_bucket = longest_context > 256 ? std::min(16, (longest_context + 127) / 128) : 0;
+    const uint64_t key = (uint64_t)T | ((uint64_t)W << 16) | ((uint64_t)ctx_bucket << 32) | ((uint64_t)want_ids << 40);
+    rc = B200_OK;
+    auto it = graph_ok ? graphs_.find(key) : graphs_.end();
+    if (it != graphs_.end()) {
+        if (cudaGraphLaunch(it->second.exec, stream_) != cudaSuccess) { err = "step: graph launch failed"; return B200_EINVAL; }
+        count_launch(it->second.launches);
+    } else if (graph_ok && ++graph_seen_[key] >= 2) {
+        const uint64_t before = b200_launch_count();
+        capturing_ = true;
+        cudaGraph_t g = nullptr;
+        if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+            const cudaError_t ce = cudaStreamEndCapture(stream_, &g);
+            capturing_ = false;
+            cudaGraphExec_t exec = nullptr;
+            if (rc == B200_OK && ce == cudaSuccess && g && cudaGraphInstantiate(&exec, g, 0) == cudaSuccess) {
+                graphs_[key] = {exec, (int)(b200_launch_count() - before)};
+                if (cudaGraphLaunch(exec, stream_) != cudaSuccess) { err = "step: graph launch failed"; return B200_EINVAL; }
+            } else {   // not capturable here: run the launches directly, and do not try again
+                cudaGetLastError();
+                graphs_enabled_ = false;
+                rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+            }
+            if (g) cudaGraphDestroy(g);
+        } else {
+            capturing_ = false;
+            cudaGetLastError();
+            graphs_enabled_ = false;
+            rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+        }
+    } else
+        rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+    if (rc != B200_OK) return rc;
+    if (W > 0) {
+        if (logits_out) cudaMemcpyAsync(logits_host_, logits_, (size_t)W * vocab_ * 4, cudaMemcpyDeviceToHost, stream_);
+        if (ids_out) cudaMemcpyAsync(ids_out, ids_dev_, (size_t)W * 4, cudaMemcpyDeviceToHost, stream_);
+    }
+    const cudaError_t e = cudaStreamSynchronize(stream_);
+    if (e != cudaSuccess) { err = std::string("step: ") + cudaGetErrorString(e); return (int)e; }
+    if (W > 0 && logits_out) memcpy(logits_out, logits_host_, (size_t)W * vocab_ * 4);
+    launches_ = (int)(b200_launch_count() - launches0);
     return B200_OK;
 }
 

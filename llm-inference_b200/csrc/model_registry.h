@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdint>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -113,6 +115,73 @@ public:
     virtual int capture_layers(int) { return B200_EUNSUPPORTED; }
     virtual int captured_layers(float*, size_t) { return B200_EUNSUPPORTED; }
     virtual int step_launches() const { return 0; }
+};
+
+// What the families that serve config.json + model.safetensors checkpoints share around their launch sequence: the
+// stream, the sequence batch behind the Model interface, the workspaces that grow with the largest step seen, the copy of
+// the residual stream after every layer run, CUDA-graph replay of repeated single-token steps, and the way logits and
+// greedy picks reach the host. A family supplies enqueue() (every launch of a step, in order, on stream_: no
+// synchronisation, no allocation, so that it can be captured), ensure_scratch() (its own buffers, among them logits_ and
+// ids_dev_) and step_workspace_bytes() (what its attention / recurrence kernels want as shared workspace).
+class StepRunner : public Model {
+public:
+    ~StepRunner() override;
+    int vocab() const override { return vocab_; }
+    int width() const override { return D_; }
+    int n_slots() const override { return seq_.n_slots; }
+    int max_positions() const override { return seq_.max_positions; }
+    int page_rows() const override { return seq_.pool.page_rows(); }
+    int pages_total() const override { return seq_.pool.n_pages(); }
+    int pages_free() const override { return seq_.pool.free_count(); }
+    int slot_length(int slot) const override { return seq_.length[slot]; }
+    int slot_page_count(int slot) const override { return seq_.pool.owned(slot); }
+    int slot_pages(int slot, int* out, int max_n) const override;
+    int step_launches() const override { return launches_; }
+    int step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) override;
+    int release(int slot) override;
+    int capture_layers(int on) override { capture_on_ = on != 0; return B200_OK; }
+    int captured_layers(float* out, size_t max_floats) override;
+
+protected:
+    virtual int enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err) = 0;
+    virtual int ensure_scratch(int T, int W) = 0;
+    virtual size_t step_workspace_bytes(int T, int n_entries) const = 0;
+    // stream_ and the graph switch (B200_NO_GRAPH=1: every step as plain launches)
+    int init_runner(std::string& err);
+    size_t esz() const { return dtype_ == B200_BF16 ? 2 : 4; }
+    void* dalloc(size_t bytes);   // device memory owned until the model closes
+    // y[M, N] = A[M, K] W[N, K]^T, contiguous; A and W of the serving dtype: the tcgen05 GEMM when it fits, else the grouped one
+    int gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi = B200_GG_NONE);
+    // the host buffer of the logits follows the largest number of wanted places (called from ensure_scratch)
+    int ensure_logits_host(int W);
+    void buffers_moved() { ++buffers_epoch_; }   // a buffer that captured launches point into was reallocated
+    void keep_layer(size_t run, const float* x, int T);   // inside enqueue, after a layer run
+
+    int dtype_ = B200_BF16, vocab_ = 0, D_ = 0;
+    SequenceBatch seq_;
+    cudaStream_t stream_ = nullptr;
+    void* ws_ = nullptr;        // split-K partials of the weight-streaming GEMM
+    size_t ws_bytes_ = 0;
+    void* attn_ws_ = nullptr;   // shares of split attention contexts / chunk summaries of a recurrence
+    size_t attn_ws_bytes_ = 0;
+    float* logits_ = nullptr;   // device, inside the family's scratch
+    int* ids_dev_ = nullptr;
+    bool capture_on_ = false, capturing_ = false;
+
+private:
+    void drop_graphs();
+    std::vector<void*> owned_;
+    float* logits_host_ = nullptr;
+    size_t logits_host_floats_ = 0;
+    struct StepGraph { cudaGraphExec_t exec; int launches; };
+    std::map<uint64_t, StepGraph> graphs_;
+    std::map<uint64_t, int> graph_seen_;
+    uint64_t buffers_epoch_ = 0, graph_epoch_ = 0;
+    const int* graph_tables_ = nullptr;   // the per-step tables the graphs read
+    bool graphs_enabled_ = true;
+    float* capture_ = nullptr;
+    size_t capture_cap_ = 0;
+    int captured_tokens_ = 0, launches_ = 0;
 };
 
 using ModelFactory = Model* (*)(const ModelDir& dir, const b200_model_options& opt, std::string& err);

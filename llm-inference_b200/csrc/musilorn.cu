@@ -9,8 +9,9 @@
 // A span of layers ("loop") runs several times with the same weights; every pass starts with x <- W_in [x; embedding],
 // and every layer RUN (not every layer) owns its cache pages or state. The logits are tanh-capped.
 //
-// A step runs on the family-independent pieces of the library: SequenceBatch / PagePool for slots, pages and the
-// per-token tables, SlotState for what is carried per slot, b200_layernorm_pair / b200_layernorm_residual,
+// A step runs on the family-independent pieces of the library: StepRunner (stream, workspaces, graph replay of single-token
+// steps, results to the host), SequenceBatch / PagePool for slots, pages and the per-token tables, SlotState for what is
+// carried per slot, b200_layernorm_pair / b200_layernorm_residual,
 // b200_linear_ex (tcgen05) and b200_gemm_grouped, b200_rope_angles, b200_qk_prepare, b200_paged_attention,
 // b200_retention. The residual stream, all norms, the softmax, the recurrence and everything entering it are fp32 in
 // both serving dtypes; in B200_BF16 the GEMM operands and the caches are bfloat16.
@@ -68,71 +69,29 @@ struct MuRun {
     SlotState state;                             // attention: ring of conv inputs; retention: S
 };
 
-class Musilorn : public Model {
+class Musilorn : public StepRunner {
 public:
     ~Musilorn() override {
         if (stream_) cudaStreamSynchronize(stream_);
-        drop_graphs();
-        for (void* p : owned_) cudaFree(p);
         cudaFree(scratch_);
-        cudaFree(ws_);
-        cudaFree(attn_ws_);
-        cudaFree(capture_);
-        if (logits_host_) cudaFreeHost(logits_host_);
-        if (stream_) cudaStreamDestroy(stream_);
     }
     const char* family() const override { return "Musilorn"; }
-    int vocab() const override { return vocab_; }
-    int width() const override { return D_; }
     int layer_count() const override { return (int)runs_.size(); }   // layer runs: what a step executes and captures
-    int n_slots() const override { return seq_.n_slots; }
-    int max_positions() const override { return seq_.max_positions; }
-    int page_rows() const override { return seq_.pool.page_rows(); }
-    int pages_total() const override { return seq_.pool.n_pages(); }
-    int pages_free() const override { return seq_.pool.free_count(); }
-    int slot_length(int slot) const override { return seq_.length[slot]; }
-    int slot_page_count(int slot) const override { return seq_.pool.owned(slot); }
-    int slot_pages(int slot, int* out, int max_n) const override {
-        const int n = std::min(max_n, seq_.pool.owned(slot));
-        for (int i = 0; i < n; ++i) out[i] = seq_.pool.list(slot)[i];
-        return n;
-    }
-    int step_launches() const override { return launches_; }
 
     int load(const ModelDir& dir, const b200_model_options& opt, std::string& err);
-    int step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) override;
-    int release(int slot) override {
-        cudaStreamSynchronize(stream_);   // pages and state change owner only behind the work that reads them
-        return seq_.release(slot);
-    }
-    int capture_layers(int on) override { capture_on_ = on != 0; return B200_OK; }
-    int captured_layers(float* out, size_t max_floats) override {
-        const size_t n = (size_t)runs_.size() * captured_tokens_ * D_;
-        if (!capture_ || n == 0) return 0;
-        if (n > max_floats) return B200_EWORKSPACE;
-        cudaStreamSynchronize(stream_);
-        if (cudaMemcpy(out, capture_, n * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) return B200_EINVAL;
-        return captured_tokens_;
-    }
 
 private:
-    size_t esz() const { return dtype_ == B200_BF16 ? 2 : 4; }
-    void* dalloc(size_t bytes) {
-        void* p = nullptr;
-        if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) return nullptr;
-        owned_.push_back(p);
-        return p;
-    }
     int parse_rot(const Json& mx, int dim, int layout, MuRot& rot, std::string& err);
-    int gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi = B200_GG_NONE);
-    int ensure_scratch(int T, int W);
-    int enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err);
-    void drop_graphs() {
-        for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);
-        graphs_.clear();
+    int ensure_scratch(int T, int W) override;
+    int enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err) override;
+    size_t step_workspace_bytes(int T, int n_entries) const override {
+        size_t need = 0;
+        for (const MuLayer& L : layers_)
+            need = std::max(need, L.attention ? b200_paged_attention_workspace_bytes(T, L.heads, L.vdim)
+                                              : b200_retention_workspace_bytes(T, n_entries, L.heads, L.dim, L.vdim));
+        return need;
     }
 
-    int dtype_ = B200_BF16, vocab_ = 0, D_ = 0;
     float eps_ = 1e-5f, mult_ = 1.f, logit_cap_ = 0.f;
     std::vector<MuLayer> layers_;
     std::vector<MuRun> runs_;
@@ -140,36 +99,14 @@ private:
     bool has_loop_ = false;
     void *embed_ = nullptr, *head_ = nullptr, *loop_in_ = nullptr;
     float *fnw_ = nullptr, *fnb_ = nullptr;
-    SequenceBatch seq_;
-    std::vector<void*> owned_;
-    cudaStream_t stream_ = nullptr;
     // scratch, grown to the largest step seen
     char* scratch_ = nullptr;
-    void* ws_ = nullptr;   // split-K partials of the weight-streaming GEMM
-    size_t ws_bytes_ = 0;
-    void* attn_ws_ = nullptr;   // shares of split attention contexts / chunk states of retention
-    size_t attn_ws_bytes_ = 0;
     int cap_T_ = 0, cap_W_ = 0;
     float *gu_ = nullptr;   // [gate | up] of small batches before the activation
-    float *x_ = nullptr, *x0_ = nullptr, *proj_ = nullptr, *y_ = nullptr, *ret_ = nullptr, *logits_ = nullptr, *cs_ = nullptr;
+    float *x_ = nullptr, *x0_ = nullptr, *proj_ = nullptr, *y_ = nullptr, *ret_ = nullptr, *cs_ = nullptr;
     void *h1_ = nullptr, *h2_ = nullptr, *cat_ = nullptr, *q_ = nullptr, *att_ = nullptr, *act_ = nullptr, *hf_ = nullptr;
-    int* ids_dev_ = nullptr;
-    float* logits_host_ = nullptr;
-    size_t logits_host_floats_ = 0;
     int max_in_ = 0, max_q_ = 0, max_att_ = 0, max_ff_ = 0, freq_floats_ = 0;   // maxima over layers (scratch sizes)
     std::vector<int> freq_off_;   // first float of each frequency set's cos table in cs_ (per token: see step)
-    // CUDA graphs of single-token steps, by batch shape
-    struct StepGraph { cudaGraphExec_t exec; int launches; };
-    std::map<uint64_t, StepGraph> graphs_;
-    std::map<uint64_t, int> graph_seen_;
-    uint64_t buffers_epoch_ = 0, graph_epoch_ = 0;   // bumped whenever a buffer the captured launches point into is reallocated
-    const int* graph_tables_ = nullptr;              // the per-step tables the graphs read
-    bool graphs_enabled_ = true, capturing_ = false;
-    bool capture_on_ = false;
-    float* capture_ = nullptr;
-    size_t capture_cap_ = 0;
-    int captured_tokens_ = 0;
-    int launches_ = 0;
 };
 
 #define MU_TRY(call)                    \
@@ -233,11 +170,7 @@ int Musilorn::load(const ModelDir& dir, const b200_model_options& opt, std::stri
     mult_ = (float)c.number("residual_mult", 1.0);
     logit_cap_ = (float)c.number("logit_softcap", 0.0);
     if (opt.max_tokens < 1 || opt.max_slots < 1) { err = "max_tokens and max_slots must be positive"; return B200_EINVAL; }
-    if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) { err = "no CUDA device: this library has no CPU path"; return B200_EINVAL; }
-    {
-        const char* e = getenv("B200_NO_GRAPH");   // 1: every step as plain launches
-        graphs_enabled_ = !(e && e[0] == '1');
-    }
+    MU_TRY(init_runner(err));
     SafeTensorsFile st;
     if (!st.open(dir.path + "/model.safetensors", err)) return B200_EINVAL;
     // the design has no position limit of its own: a sequence can grow as long as the pool has pages
@@ -402,7 +335,7 @@ int Musilorn::ensure_scratch(int T, int W) {
     if (T <= cap_T_ && W <= cap_W_) return B200_OK;
     const int cT = std::max(T, cap_T_), cW = std::max(W, cap_W_);
     cudaStreamSynchronize(stream_);
-    ++buffers_epoch_;
+    buffers_moved();
     cudaFree(scratch_);
     scratch_ = nullptr;
     cap_T_ = cap_W_ = 0;
@@ -436,28 +369,7 @@ int Musilorn::ensure_scratch(int T, int W) {
     take(h1_); take(h2_); take(cat_); take(q_); take(att_); take(act_); take(hf_); take(ids_dev_); take(gu_);
     cap_T_ = cT;
     cap_W_ = cW;
-    const size_t lf = (size_t)cW * vocab_;
-    if (lf > logits_host_floats_) {
-        if (logits_host_) cudaFreeHost(logits_host_);
-        logits_host_ = nullptr;
-        if (cudaMallocHost(&logits_host_, lf * 4) != cudaSuccess) return B200_ENOMEM;
-        logits_host_floats_ = lf;
-    }
-    return B200_OK;
-}
-
-// y[M, N] = A[M, K] W[N, K]^T, contiguous; A and W of the serving dtype: the tcgen05 GEMM when it fits, else the grouped one
-int Musilorn::gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi) {
-    const size_t need = b200_linear_ex_workspace_bytes(M, N, K);
-    if (need > ws_bytes_ && !capturing_) {
-        cudaStreamSynchronize(stream_);
-        ++buffers_epoch_;
-        cudaFree(ws_);
-        ws_ = nullptr;
-        ws_bytes_ = 0;
-        if (cudaMalloc(&ws_, need) == cudaSuccess) ws_bytes_ = need;   // without it the call runs with a single split
-    }
-    return b200_linear_ex(A, W, C, M, N, K, dtype_, c_dt, epi, ws_, ws_bytes_, stream_);
+    return ensure_logits_host(cW);
 }
 
 // every launch of a step, in order, on stream_ (no synchronisation, no allocation: capturable into a graph)
@@ -546,8 +458,7 @@ int Musilorn::enqueue(int T, int W, int longest_entry, int longest_context, bool
             MU_OP(b200_layernorm_residual(x_, y_, T, D, eps_, mult_, L.n1bw, L.n1bb, next ? next->n1w : nullptr, next ? next->n1b : nullptr,
                                           next ? h1_ : nullptr, dt, stream_));
         h1_ready = next != nullptr;
-        if (capture_on_)
-            cudaMemcpyAsync(capture_ + r * (size_t)T * D, x_, (size_t)T * D * 4, cudaMemcpyDeviceToDevice, stream_);
+        keep_layer(r, x_, T);
     }
     if (W > 0) {
         MU_OP(b200_layernorm_pair(x_, seq_.d_want_rows(), W, D, eps_, fnw_, fnb_, hf_, nullptr, nullptr, nullptr, dt, stream_));
@@ -557,97 +468,6 @@ int Musilorn::enqueue(int T, int W, int longest_entry, int longest_context, bool
     }
     return B200_OK;
 #undef MU_OP
-}
-
-int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) {
-    if (entries.empty()) return B200_OK;
-    const uint64_t launches0 = b200_launch_count();
-    MU_TRY(seq_.begin_step(entries, stream_, err));
-    const int T = seq_.n_tokens, W = seq_.n_want, D = D_;
-    if (ensure_scratch(T, std::max(W, 1)) != B200_OK) { err = "step: out of device memory for the scratch buffers"; return B200_ENOMEM; }
-    int longest_entry = 0, longest_context = 0;
-    for (const StepEntry& en : entries) {
-        longest_entry = std::max(longest_entry, en.n_tokens);
-        longest_context = std::max(longest_context, seq_.length[en.slot]);
-    }
-    {   // room for the shares of split contexts (batches of few rows) and for the chunk states of long retention entries
-        size_t need = 0;
-        for (const MuLayer& L : layers_)
-            need = std::max(need, L.attention ? b200_paged_attention_workspace_bytes(T, L.heads, L.vdim)
-                                              : b200_retention_workspace_bytes(T, seq_.n_entries, L.heads, L.dim, L.vdim));
-        if (need > attn_ws_bytes_) {
-            cudaStreamSynchronize(stream_);
-            ++buffers_epoch_;
-            cudaFree(attn_ws_);
-            attn_ws_ = nullptr;
-            attn_ws_bytes_ = 0;
-            if (cudaMalloc(&attn_ws_, need) == cudaSuccess) attn_ws_bytes_ = need;
-        }
-    }
-    if (capture_on_) {
-        const size_t need = (size_t)runs_.size() * T * D;
-        if (capture_cap_ < need) {
-            cudaStreamSynchronize(stream_);
-            cudaFree(capture_);
-            capture_ = nullptr;
-            if (cudaMalloc(&capture_, need * 4) != cudaSuccess) { err = "step: no memory to keep the layers"; return B200_ENOMEM; }
-            capture_cap_ = need;
-        }
-        captured_tokens_ = T;
-    }
-    // Batches of single tokens repeat their shape step after step: the second time a shape is seen its launch sequence is
-    // captured into a CUDA graph, from then on the step is one graph launch (the per-step tables are read through fixed
-    // pointers that begin_step refreshes). Anything that moves a buffer drops the graphs.
-    const bool want_ids = ids_out != nullptr;
-    if (buffers_epoch_ != graph_epoch_ || seq_.d_ids() != graph_tables_) {   // a buffer was reallocated (even to the same address:
-        drop_graphs();                                                         // the carving inside it changed)
-        graph_epoch_ = buffers_epoch_;
-        graph_tables_ = seq_.d_ids();
-    }
-    const bool graph_ok = graphs_enabled_ && longest_entry == 1 && !capture_on_ && T <= 4096 && W <= 4096;
-    const int ctx_bucket = longest_context > 256 ? std::min(16, (longest_context + 127) / 128) : 0;
-    const uint64_t key = (uint64_t)T | ((uint64_t)W << 16) | ((uint64_t)ctx_bucket << 32) | ((uint64_t)want_ids << 40);
-    int rc = B200_OK;
-    auto it = graph_ok ? graphs_.find(key) : graphs_.end();
-    if (it != graphs_.end()) {
-        if (cudaGraphLaunch(it->second.exec, stream_) != cudaSuccess) { err = "step: graph launch failed"; return B200_EINVAL; }
-        count_launch(it->second.launches);
-    } else if (graph_ok && ++graph_seen_[key] >= 2) {
-        const uint64_t before = b200_launch_count();
-        capturing_ = true;
-        cudaGraph_t g = nullptr;
-        if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-            rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
-            const cudaError_t ce = cudaStreamEndCapture(stream_, &g);
-            capturing_ = false;
-            cudaGraphExec_t exec = nullptr;
-            if (rc == B200_OK && ce == cudaSuccess && g && cudaGraphInstantiate(&exec, g, 0) == cudaSuccess) {
-                graphs_[key] = {exec, (int)(b200_launch_count() - before)};
-                if (cudaGraphLaunch(exec, stream_) != cudaSuccess) { err = "step: graph launch failed"; return B200_EINVAL; }
-            } else {   // not capturable here: run the launches directly, and do not try again
-                cudaGetLastError();
-                graphs_enabled_ = false;
-                rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
-            }
-            if (g) cudaGraphDestroy(g);
-        } else {
-            capturing_ = false;
-            cudaGetLastError();
-            graphs_enabled_ = false;
-            rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
-        }
-    } else
-        rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
-    if (rc != B200_OK) return rc;
-    if (W > 0) {
-        if (logits_out) cudaMemcpyAsync(logits_host_, logits_, (size_t)W * vocab_ * 4, cudaMemcpyDeviceToHost, stream_);
-        if (ids_out) cudaMemcpyAsync(ids_out, ids_dev_, (size_t)W * 4, cudaMemcpyDeviceToHost, stream_);
-    }
-    const cudaError_t e = cudaStreamSynchronize(stream_);
-    if (e != cudaSuccess) { err = std::string("step: ") + cudaGetErrorString(e); return (int)e; }
-    if (W > 0 && logits_out) memcpy(logits_out, logits_host_, (size_t)W * vocab_ * 4);
-    launches_ = (int)(b200_launch_count() - launches0);
-    return B200_OK;
 }
 
 Model* make_musilorn(const ModelDir& dir, const b200_model_options& opt, std::string& err) {
