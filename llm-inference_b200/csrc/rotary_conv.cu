@@ -2,6 +2,8 @@
 // one table per frequency set), the short causal convolution over time with its carried inputs, the per-head RMS norm,
 // the rotation in either pairing, and the store of q, k (and of the convolved keys as values) — b200_qk_prepare — plus
 // the update of the convolution's ring of carried inputs. All arithmetic fp32; only the stores take the serving dtype.
+#include <cuda_bf16.h>
+
 #include "b200_serve.h"
 #include "common.cuh"
 #include "launch_count.h"
@@ -143,6 +145,49 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
         dst[i] = DT<T>::from_f(rotary_component(vals, i, a.rot_dims, a.rot_layout, a.cos + (size_t)t * nf, a.sin + (size_t)t * nf));
 }
 
+// Without convolution and head norm the preparation is a rotation and three scatters: a thread per four consecutive
+// dimensions of one head (or value head) of one token. It loads its own four values and, inside the rotated part, the
+// four of its rotate-half partner with 16-byte loads, and stores four values of the serving dtype at once.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_rotate_store_kernel(const QkPrep a, long long total, int quads_per_token) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int t = (int)(idx / quads_per_token), qd = (int)(idx % quads_per_token);
+    const int dim = a.dim, qk_quads = (a.heads + a.kv_heads) * (dim / 4);
+    const float* row = a.proj + (size_t)t * a.ld_proj;
+    float4 v;
+    T* dst;
+    if (qd < qk_quads) {
+        const int u = qd / (dim / 4), i0 = (qd % (dim / 4)) * 4, half = a.rot_dims / 2;
+        v = *reinterpret_cast<const float4*>(row + (size_t)u * dim + i0);
+        if (i0 < a.rot_dims) {
+            const bool low = i0 < half;
+            const float4 w = *reinterpret_cast<const float4*>(row + (size_t)u * dim + (low ? i0 + half : i0 - half));
+            const float* cs = a.cos + (size_t)t * half + (low ? i0 : i0 - half);
+            const float* sn = a.sin + (size_t)t * half + (low ? i0 : i0 - half);
+            // the pair (lo, hi) becomes (lo c - hi s, hi c + lo s)
+            if (low) v = make_float4(v.x * cs[0] - w.x * sn[0], v.y * cs[1] - w.y * sn[1], v.z * cs[2] - w.z * sn[2], v.w * cs[3] - w.w * sn[3]);
+            else v = make_float4(v.x * cs[0] + w.x * sn[0], v.y * cs[1] + w.y * sn[1], v.z * cs[2] + w.z * sn[2], v.w * cs[3] + w.w * sn[3]);
+        }
+        if (u < a.heads) dst = reinterpret_cast<T*>(a.q_out) + ((size_t)t * a.heads + u) * dim + i0;
+        else {
+            const int p = a.pos[t];
+            const size_t prow = (size_t)a.pages[(size_t)a.slot[t] * a.max_pages + p / a.page_rows] * a.page_rows + p % a.page_rows;
+            dst = reinterpret_cast<T*>(a.k_pool) + (prow * a.kv_heads + (u - a.heads)) * dim + i0;
+        }
+    } else {
+        const int c0 = (qd - qk_quads) * 4, p = a.pos[t];   // value column (head g, dimension c0 % vdim)
+        v = *reinterpret_cast<const float4*>(row + a.v_off + c0);
+        const size_t prow = (size_t)a.pages[(size_t)a.slot[t] * a.max_pages + p / a.page_rows] * a.page_rows + p % a.page_rows;
+        dst = reinterpret_cast<T*>(a.v_pool) + prow * a.v_heads * a.vdim + c0;
+    }
+    if constexpr (sizeof(T) == 4) *reinterpret_cast<float4*>(dst) = v;
+    else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+}
+
 __global__ void conv_state_update_kernel(const float* __restrict__ proj, long long ld_proj, float* __restrict__ state,
                                          const int* __restrict__ slot, const int* __restrict__ pos, const int* __restrict__ end,
                                          int channels, int taps) {
@@ -184,12 +229,28 @@ extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
              p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->update_state_inline ? const_cast<float*>(p->conv_state) : nullptr, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
              p->start, p->heads, p->kv_heads, p->dim, p->v_heads, p->vdim, p->v_off};
     if (a.conv_w && a.taps == 1) a.conv_state = a.proj;   // never read: every input of a one-tap filter is the token's own
+    cudaStream_t s = (cudaStream_t)stream;
+    {   // rotation and scatters only, everything in whole groups of four: the vector kernel
+        auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+        const bool plain = !p->conv_w && !p->q_norm && !p->k_norm && p->rot_layout == B200_ROPE_HALF && p->dim % 4 == 0 && p->rot_dims % 8 == 0 &&
+                           p->ld_proj % 4 == 0 && al16(p->proj) && al16(p->q_out) && al16(p->k_pool) &&
+                           (p->v_heads == 0 || (p->vdim % 4 == 0 && p->v_off % 4 == 0 && al16(p->v_pool))) &&
+                           (p->dtype == B200_BF16 || p->dtype == B200_F32);
+        if (plain) {
+            const int quads = (p->heads + p->kv_heads) * (p->dim / 4) + p->v_heads * (p->vdim / 4);
+            const long long total = (long long)p->n_tokens * quads;
+            const unsigned grid = (unsigned)((total + 255) / 256);
+            if (p->dtype == B200_BF16) qk_rotate_store_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, total, quads);
+            else qk_rotate_store_kernel<float><<<grid, 256, 0, s>>>(a, total, quads);
+            count_launch();
+            return (int)cudaGetLastError();
+        }
+    }
     const long long units = (long long)p->n_tokens * (p->heads + p->kv_heads + p->v_heads);
     if (units > 0x7fffffffll) return B200_EUNSUPPORTED;
     const unsigned grid = (unsigned)((units + kPrepWarps - 1) / kPrepWarps);
     const size_t smem = (size_t)kPrepWarps * p->dim * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
-    cudaStream_t s = (cudaStream_t)stream;
     if (p->dtype == B200_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, kPrepWarps * 32, smem, s>>>(a, (int)units);
     else if (p->dtype == B200_F32) qk_prepare_kernel<float><<<grid, kPrepWarps * 32, smem, s>>>(a, (int)units);
     else return B200_EINVAL;

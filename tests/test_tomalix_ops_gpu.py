@@ -214,19 +214,24 @@ def test_a_key_at_the_edge_of_a_block(S, kind, chunk, edge):
 
 
 @pytest.mark.parametrize("kind", ["f32", "bf16"])
-def test_qk_prepare_stores_projected_values(S, kind):
-    """two score maps per head as twice the heads, partial rotate-half rotation with an amplitude, values copied as they are"""
+@pytest.mark.parametrize("H,G,maps,d,dv,rot,pad", [(3, 1, 2, 10, 6, 4, 3), (3, 1, 2, 16, 8, 8, 4), (2, 2, 1, 64, 128, 64, 0), (4, 2, 1, 32, 32, 0, 8),
+                                                     (2, 1, 1, 24, 20, 16, 4), (2, 1, 1, 16, 8, 12, 0)])
+def test_qk_prepare_stores_projected_values(S, kind, H, G, maps, d, dv, rot, pad):
+    """two score maps per head as twice the heads, partial rotate-half rotation with an amplitude, values copied as they are;
+    sizes in whole groups of four take the vector kernel, the others (and a rotated part of 12) the warp-per-head one"""
     code, g = code_of(S, kind), gen(3)
-    H, G, maps, d, dv, PR, rot = 3, 1, 2, 10, 6, 4, 4
+    PR = 4
     lens = {0: 9, 1: 5}
-    n_in = H * maps * d + G * maps * d + G * dv + 3          # three unrelated columns behind the values
+    n_in = H * maps * d + G * maps * d + G * dv + pad        # unrelated columns behind the values
     rows = [(b, p) for b, n in lens.items() for p in range(n)]
     T = len(rows)
     proj = torch.randn(T, n_in, generator=g)
-    f, amp = O.rot_frequencies(dict(dims=rot, base=100.0, scaling=dict(factor=2.0, original=16, fast=4.0, slow=1.0)), "ramp")
+    sc = dict(dims=rot, base=100.0, scaling=dict(factor=2.0, original=16, fast=4.0, slow=1.0))
     slot, pos = [b for b, _ in rows], [p for _, p in rows]
-    cs, sn = torch.zeros(T, rot // 2, device="cuda"), torch.zeros(T, rot // 2, device="cuda")
-    sync_ok(S.lib().b200_rope_angles_amp(ints(pos).data_ptr(), T, dev(f).data_ptr(), rot // 2, amp, cs.data_ptr(), sn.data_ptr(), None))
+    cs, sn = torch.zeros(T, max(rot // 2, 1), device="cuda"), torch.zeros(T, max(rot // 2, 1), device="cuda")
+    if rot:
+        f, amp = O.rot_frequencies(sc, "ramp")
+        sync_ok(S.lib().b200_rope_angles_amp(ints(pos).data_ptr(), T, dev(f).data_ptr(), rot // 2, amp, cs.data_ptr(), sn.data_ptr(), None))
     table = dev(torch.tensor([[2, 0, 5], [4, 1, 3]], dtype=torch.int32))
     kp = torch.full((6 * PR, G * maps, d), 7.0, dtype=tdt(S, code), device="cuda")
     vp = torch.full((6 * PR, G, dv), 7.0, dtype=tdt(S, code), device="cuda")
@@ -239,7 +244,6 @@ def test_qk_prepare_stores_projected_values(S, kind):
     tol = 1e-2 if kind == "bf16" else 1e-6
     for b, n in lens.items():
         idx = [i for i, (bb, _) in enumerate(rows) if bb == b]
-        sc = dict(dims=rot, base=100.0, scaling=dict(factor=2.0, original=16, fast=4.0, slow=1.0))
         wq = O.rotate_half(proj[idx, : H * maps * d].double().reshape(n, H * maps, d), sc, "ramp")
         wk = O.rotate_half(proj[idx, H * maps * d: v_off].double().reshape(n, G * maps, d), sc, "ramp")
         assert rel(qo[idx].float().reshape(n, H * maps, d), wq) < tol
