@@ -236,8 +236,8 @@ def test_pages_slots_and_states_used_again(S, models, kind):
         gb = [m.step([(1, b[:10], list(range(10)))])]
         out = m.step([(0, a[60:], list(range(40))), (1, b[10:], list(range(40)))])
         ga.append(out[:40]); gb.append(out[40:])
-        check(np.concatenate(ga), oracle.forward(a).numpy(), kind, f"round {rnd} a")
-        check(np.concatenate(gb), oracle.forward(b).numpy(), kind, f"round {rnd} b")
+        check(np.concatenate(ga), oracle.forward(a).numpy(), kind, f"turn {rnd}, first request")
+        check(np.concatenate(gb), oracle.forward(b).numpy(), kind, f"turn {rnd}, second request")
         free = m.pages_free
         with pytest.raises(RuntimeError):
             m.step([(1, tokens(80, V, 1), [0])])          # 50 + 80 tokens need a third page for slot 1: none left
