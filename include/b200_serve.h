@@ -108,6 +108,9 @@ int b200_moe_route_logits(const void* h, int h_dtype, const float* w_router, con
  * rows). One launch, no host sync. */
 int b200_moe_dispatch(const int* chosen, int n_tokens, int top, int n_experts, int* group_off, int* src_row, int* dest,
                       void* stream);
+/* dst[i, :] = src[rows[i], :] (both of `dtype`, contiguous rows of `width`): the sorted rows of b200_moe_dispatch side by side,
+ * so that a dense GEMM can read one expert's group */
+int b200_gather_rows(const void* src, const int* rows, void* dst, int n_rows, int width, int dtype, void* stream);
 /* x[t,:] += mix[t,:] + shared[t,:] + sum_k weight[t,k] * (dest[t,k] >= 0 ? expert_out[dest[t,k],:] : h[t,:])
  * (fp32 sums in a fixed order; mix, shared, the routed part may each be NULL) */
 int b200_residual_combine(float* x, const float* mix, const float* shared, const float* expert_out, const int* dest,

@@ -137,9 +137,31 @@ __global__ void __launch_bounds__(256) residual_combine_kernel(float* __restrict
     }
 }
 
+// dst[i, :] = src[rows[i], :]: the rows of every expert's group side by side, so that a dense GEMM can read a group
+__global__ void __launch_bounds__(256) gather_rows_kernel(const unsigned char* __restrict__ src, const int* __restrict__ rows,
+                                                         unsigned char* __restrict__ dst, size_t row_bytes, int vec) {
+    const unsigned char* s = src + (size_t)rows[blockIdx.x] * row_bytes;
+    unsigned char* d = dst + (size_t)blockIdx.x * row_bytes;
+    if (vec) {
+        for (size_t i = (size_t)threadIdx.x * 16; i < row_bytes; i += (size_t)blockDim.x * 16) st16(d + i, ld16(s + i));
+    } else {
+        for (size_t i = threadIdx.x; i < row_bytes; i += blockDim.x) d[i] = s[i];
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_gather_rows(const void* src, const int* rows, void* dst, int n_rows, int width, int dtype, void* stream) {
+    if (!src || !rows || !dst || n_rows < 0 || width < 1 || (dtype != B200_BF16 && dtype != B200_F32)) return B200_EINVAL;
+    if (n_rows == 0) return B200_OK;
+    const size_t row_bytes = (size_t)width * (dtype == B200_BF16 ? 2 : 4);
+    const int vec = row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+    gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>((const unsigned char*)src, rows, (unsigned char*)dst, row_bytes, vec);
+    count_launch();
+    return (int)cudaGetLastError();
+}
 
 extern "C" int b200_moe_route(const void* h, int h_dtype, const float* w_router, const float* correction, int n_tokens,
                               int width, int n_out, int top, float scale, int* chosen, float* weight, void* stream) {

@@ -6,10 +6,12 @@
 //
 //   conv_act_kernel          a thread per (token, channel): taps from this step's rows, the slot's ring or zeros.
 //   selective_scan_kernel    a group of LP lanes owns one channel of one entry (a run of consecutive tokens of a
-//                            sequence) and walks its tokens; a lane keeps up to 8 states in registers (state n of lane l
-//                            is l + k LP, so the B / C rows are read with consecutive lanes on consecutive addresses) and
-//                            the channel's output is a shuffle sum over the group. Long entries are cut into chunks that
-//                            run in parallel (further down).
+//                            sequence) and walks its tokens; a lane keeps up to 8 states in registers (eight consecutive
+//                            ones behind 16-byte B / C loads when the state count fills the lanes, else state n of lane l
+//                            is l + k LP behind predicated loads) and the channel's output is a shuffle sum over the group.
+//                            Entries of 256 tokens or more are cut into chunks of 64 that run in parallel: chunk-local
+//                            scans from zero, scan_carry_kernel over their summaries, then every chunk again from its
+//                            true start state with outputs. bfloat16 serving takes exp(dt A) as exp2 of a pre-scaled A.
 #include <cuda_bf16.h>
 
 #include <algorithm>

@@ -91,6 +91,10 @@ class Tomalix : public StepRunner {
 public:
     ~Tomalix() override {
         if (stream_) cudaStreamSynchronize(stream_);
+        for (cudaStream_t s : side_) { cudaStreamSynchronize(s); cudaStreamDestroy(s); }
+        for (cudaEvent_t e : joined_) cudaEventDestroy(e);
+        if (forked_) cudaEventDestroy(forked_);
+        if (group_off_host_) cudaFreeHost(group_off_host_);
         cudaFree(scratch_);
     }
     const char* family() const override { return "Tomalix"; }
@@ -101,6 +105,7 @@ public:
 private:
     int parse_attn(const Json& mx, const std::string& where, int maps, bool ramp_allowed, TxAttn& at, std::string& err);
     int ensure_scratch(int T, int W) override;
+    int experts_on_side_streams(const TxLayer& L, int T, std::string& err);
     int enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err) override;
     size_t step_workspace_bytes(int T, int n_entries) const override {
         size_t need = 0;
@@ -125,6 +130,12 @@ private:
           *dtr_ = nullptr, *eo_ = nullptr, *weight_ = nullptr, *cs_ = nullptr;
     void *h1_ = nullptr, *h2_ = nullptr, *q_ = nullptr, *att_ = nullptr, *xc_ = nullptr, *sy_ = nullptr, *act_ = nullptr, *hf_ = nullptr;
     int *chosen_ = nullptr, *group_off_ = nullptr, *src_row_ = nullptr, *dest_ = nullptr;
+    // prompt steps: every expert's group as dense GEMMs of its own, spread over side streams
+    void* gath_ = nullptr;
+    int* group_off_host_ = nullptr;   // pinned
+    std::vector<cudaStream_t> side_;
+    std::vector<cudaEvent_t> joined_;
+    cudaEvent_t forked_ = nullptr;
     // maxima over layers (scratch sizes)
     int max_in_ = 0, max_q_ = 0, max_attf_ = 0, max_att_ = 0, max_inner_ = 0, max_bc_ = 0, max_act_ = 0, max_top_ = 0, max_experts_ = 0,
         freq_floats_ = 0;
@@ -454,6 +465,7 @@ int Tomalix::ensure_scratch(int T, int W) {
         al(t * std::max(1, max_inner_) * E),       // xc
         al(t * std::max(1, max_inner_) * E),       // sy
         al(t * std::max(1, max_act_) * E),         // act
+        al(t * top * D_ * E),                      // gath
         al((size_t)cW * D_ * E),                   // hf
         al(t * top * 4),                           // chosen
         al((size_t)(max_experts_ + 2) * 4),        // group_off
@@ -469,11 +481,57 @@ int Tomalix::ensure_scratch(int T, int W) {
     auto take = [&](auto*& dst) { dst = reinterpret_cast<std::remove_reference_t<decltype(dst)>>(p); p += sizes[k++]; };
     take(x_); take(x0_); take(proj_); take(y_); take(y2_); take(attf_); take(xc32_); take(bc_); take(dtr_); take(eo_); take(weight_);
     take(logits_); take(cs_);
-    take(h1_); take(h2_); take(q_); take(att_); take(xc_); take(sy_); take(act_); take(hf_);
+    take(h1_); take(h2_); take(q_); take(att_); take(xc_); take(sy_); take(act_); take(gath_); take(hf_);
     take(chosen_); take(group_off_); take(src_row_); take(dest_); take(ids_dev_);
     cap_T_ = cT;
     cap_W_ = cW;
     return ensure_logits_host(cW);
+}
+
+// Routed experts of a prompt step. With hundreds of rows per expert the groups are dense GEMMs in their own right: the
+// group sizes come to the host (one small copy and a synchronisation: a prompt step is not captured into a graph), the
+// sorted rows are gathered side by side, and every expert's up (squared relu) and down products run on the tcgen05 GEMM,
+// spread over side streams so that products of a few dozen tiles each fill the GPU together. Single-token steps and
+// small prompts stay on the grouped kernel, which needs no host round trip.
+constexpr int kExpertStreamsFrom = 1024, kExpertStreams = 4;
+int Tomalix::experts_on_side_streams(const TxLayer& L, int T, std::string& err) {
+    const int D = D_, dt = dtype_, E = L.experts;
+    const size_t ez = esz();
+    if (side_.empty()) {
+        if (cudaEventCreateWithFlags(&forked_, cudaEventDisableTiming) != cudaSuccess) { err = "cudaEventCreate"; return B200_EINVAL; }
+        for (int k = 0; k < kExpertStreams; ++k) {
+            cudaStream_t s = nullptr;
+            cudaEvent_t e = nullptr;
+            if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { err = "cudaStreamCreate"; return B200_EINVAL; }
+            side_.push_back(s);
+            joined_.push_back(e);
+        }
+    }
+    if (!group_off_host_ && cudaMallocHost(&group_off_host_, (size_t)(max_experts_ + 2) * sizeof(int)) != cudaSuccess) { err = "cudaMallocHost"; return B200_ENOMEM; }
+    cudaMemcpyAsync(group_off_host_, group_off_, (size_t)(E + 1) * sizeof(int), cudaMemcpyDeviceToHost, stream_);
+    int rc = b200_gather_rows(h2_, src_row_, gath_, T * L.top, D, dt, stream_);
+    if (rc != B200_OK) { err = "b200_gather_rows failed"; return rc; }
+    cudaEventRecord(forked_, stream_);
+    if (cudaStreamSynchronize(stream_) != cudaSuccess) { err = "step: synchronisation before the expert products failed"; return B200_EINVAL; }
+    for (cudaStream_t s : side_) cudaStreamWaitEvent(s, forked_, 0);
+    int used = 0;
+    for (int e = 0; e < E; ++e) {
+        const int off = group_off_host_[e], n = group_off_host_[e + 1] - off;
+        if (n <= 0) continue;
+        cudaStream_t s = side_[used++ % kExpertStreams];
+        // no split-K workspace: the products of different streams run at the same time and must not share one
+        rc = b200_linear_ex((const char*)gath_ + (size_t)off * D * ez, (const char*)L.w_up + (size_t)e * L.ff * D * ez,
+                            (char*)act_ + (size_t)off * L.ff * ez, n, L.ff, D, dt, dt, B200_GG_RELU2, nullptr, 0, s);
+        if (rc == B200_OK)
+            rc = b200_linear_ex((const char*)act_ + (size_t)off * L.ff * ez, (const char*)L.w_down + (size_t)e * D * L.ff * ez,
+                                eo_ + (size_t)off * D, n, D, L.ff, dt, B200_F32, B200_GG_NONE, nullptr, 0, s);
+        if (rc != B200_OK) { err = "expert product failed (" + std::to_string(rc) + ")"; break; }
+    }
+    for (int k = 0; k < kExpertStreams; ++k) {   // joined even after a failure: nothing of this step stays in flight behind stream_
+        cudaEventRecord(joined_[k], side_[k]);
+        cudaStreamWaitEvent(stream_, joined_[k], 0);
+    }
+    return rc;
 }
 
 // every launch of a step, in order, on stream_ (no synchronisation, no allocation: capturable into a graph)
@@ -594,6 +652,14 @@ int Tomalix::enqueue(int T, int W, int longest_entry, int longest_context, bool 
             } else {
                 TX_OP(b200_moe_route_logits(h2_, dt, L.router, L.router_b, T, D, L.experts, L.top, chosen_, weight_, stream_));
                 TX_OP(b200_moe_dispatch(chosen_, T, L.top, L.experts, group_off_, src_row_, dest_, stream_));
+                if (dt == B200_BF16 && !capturing_ && T >= kExpertStreamsFrom && D % 8 == 0 && L.ff % 8 == 0) {
+                    const int rc_ = experts_on_side_streams(L, T, err);
+                    if (rc_ != B200_OK) return rc_;
+                    TX_OP(boundary(nullptr, 0.f, nullptr, 0.f, true, L.top, nullptr, next ? next->n1 : nullptr, h1_));
+                    h1_ready = next != nullptr;
+                    keep_layer(r, x_, T);
+                    continue;
+                }
                 b200_gemm_grouped_args g{};
                 g.A = h2_; g.lda = D; g.a_rows = src_row_; g.group_off = group_off_;
                 g.W = L.w_up; g.ldw = D; g.stride_w = (long long)L.ff * D; g.trans_b = 1; g.epi = B200_GG_RELU2;

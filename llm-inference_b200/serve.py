@@ -103,6 +103,7 @@ SERVE_PROTOTYPES = {
     "b200_retention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "b200_retention": (_i, [C.POINTER(RetentionArgs), _vp]),
     "b200_unit_rms_gate": (_i, [_vp, _vp, _ll, _vp, _i, _i, _i, _f, _i, _vp]),
+    "b200_gather_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200_moe_route_logits": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "b200_rmsnorm_residual": (_i, [C.POINTER(RmsnormResidualArgs), _vp]),
     "b200_rope_angles_amp": (_i, [_vp, _i, _vp, _i, C.c_double, _vp, _vp, _vp]),

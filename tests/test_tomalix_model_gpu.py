@@ -280,6 +280,30 @@ def test_long_prompt_in_one_step_and_in_portions(S, models):
         m.close()
 
 
+def test_prompt_long_enough_for_dense_expert_products(S, models):
+    """1100 tokens in one step: in bfloat16 the routed experts run as dense products per expert on side streams (from 1024
+    tokens on); the same prompt in portions below that stays on the grouped kernel. Both against the oracle, and against
+    each other"""
+    folder, oracle, cfg = models["wide"]
+    toks = tokens(1100, cfg["vocab"], 8)
+    want = oracle.forward(toks).numpy()
+    m = open_model(S, folder, "bf16", max_tokens=2560)
+    whole = m.step([(0, toks, list(range(1100)))])
+    check(whole, want, "bf16", "one step")
+    got, at = [], 0
+    for c in [500, 598, 2]:
+        got.append(m.step([(1, toks[at: at + c], list(range(c)))]))
+        at += c
+    parts = np.concatenate(got)
+    check(parts, want, "bf16", "portions")
+    e = row_errors(whole, parts)
+    assert np.median(e) < 2e-2 and np.quantile(e, 0.9) < RTOL["bf16"], (float(np.median(e)), float(e.max()))
+    m.release(0)
+    again = m.step([(2, toks, list(range(1100)))])          # the side streams once more, pages in another order
+    assert err(again, whole) < 1e-6
+    m.close()
+
+
 def test_refused_configurations(S, models, tmp_path):
     folder, oracle, cfg = models["odd"]
     def refused(change, text):
