@@ -9,7 +9,10 @@
  * routed feed-forward with identity experts), "Musilorn" (sandwich-normed layers of convolved, capped attention with a
  * sink or of retention with a carried state, a span of layers run several times), "Tomalix" (pre-norm layers of
  * differential attention, of chunk-masked gated attention beside a selective scan, or of plain attention with ramped
- * frequency interpolation; dense or routed squared-relu feed-forwards; a repeated span of layers), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
+ * frequency interpolation; dense or routed squared-relu feed-forwards; a repeated span of layers), "Sakevik" (norms on the
+ * sublayers' outputs; a hashed pair embedding; layers of an element-wise gated recurrence, of windowed attention with sigmoid
+ * weights, rotated values and head gates, or of windowed latent attention with a shared rotary key part; clamped gated
+ * feed-forwards), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
  * a config.json naming the b200_model_config fields).
  */
 #ifndef B200_SERVE_H
@@ -47,6 +50,7 @@ int b200_layernorm_pair(const float* x, const int* rows, int n_rows, int width, 
 #define B200_GG_GLU_GELU 3    /* the same with gelu in its tanh form as the activation              */
 #define B200_GG_RELU2 4       /* C = max(acc, 0)^2                                                   */
 #define B200_GG_BIAS_SOFTPLUS 5 /* C = log(1 + exp(acc + aux[row, col])); ld_aux 0: a bias per column */
+#define B200_GG_GLU_CLAMP 6   /* GLU layout; g = min(gate, L), u = clamp(up, -L, L), C = g * sigmoid(1.702 g) * (u + 1), L = epi_param */
 
 typedef struct b200_gemm_grouped_args {
     const void* A; const void* W; void* C;
@@ -61,6 +65,7 @@ typedef struct b200_gemm_grouped_args {
     int trans_b;               /* 1: W is [N, K] (ldw >= K); 0: W is [K, N] (ldw >= N)                           */
     int epi;
     int a_dtype, w_dtype, c_dtype;   /* B200_F32 / B200_BF16                                                   */
+    float epi_param;           /* B200_GG_GLU_CLAMP: the limit                                                   */
 } b200_gemm_grouped_args;
 int b200_gemm_grouped(const b200_gemm_grouped_args* args, void* stream);
 
@@ -72,6 +77,9 @@ int b200_gemm_grouped(const b200_gemm_grouped_args* args, void* stream);
 size_t b200_linear_ex_workspace_bytes(int n_tokens, int N, int K);
 int b200_linear_ex(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
                    void* workspace, size_t workspace_bytes, void* stream);
+/* the same with the parameter of the epilogue (B200_GG_GLU_CLAMP: its limit) */
+int b200_linear_ex2(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
+                    float epi_param, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Latent cache rows: for token t, row = raw[t, 0:rank] (fp32, leading dimension ld_raw) divided by its root mean
  * square (eps inside the root) times w, stored as `dtype` at position pos[t] of sequence slot[t]:
@@ -93,6 +101,34 @@ int b200_latent_attention(const float* qa, float* out, const void* pool, const i
                           const int* slot, const int* pos, const float* sink, float scale, int n_tokens, int heads,
                           int rank, int dtype, int longest_entry, int longest_context, void* workspace,
                           size_t workspace_bytes, void* stream);
+
+/* The same attention with the options of designs that rotate one key part shared by all heads and look through a sliding
+ * window: pool rows are [rank + extra] wide (b200_latent_store_rot: the normed latent, then `extra` rotated key
+ * dimensions); qa and out are [n_tokens, heads, rank + extra] (qa: the absorbed query, then the head's rotated query part;
+ * of out the caller uses the first `rank` columns of every head). window > 0: position p sees the rows j with
+ * 0 <= p - j < window. sink may be NULL: plain softmax. */
+typedef struct b200_latent_attention_args {
+    const float* qa; float* out; const void* pool;
+    const int* pages; int max_pages, page_rows;
+    const int* slot; const int* pos;
+    const float* sink; float scale;
+    int n_tokens, heads, rank;       /* rank: the whole row width (latent + extra)                               */
+    int window;
+    int dtype, longest_entry, longest_context;
+    void* workspace; size_t workspace_bytes;
+} b200_latent_attention_args;
+int b200_latent_attention_ex(const b200_latent_attention_args* a, void* stream);
+/* Latent cache rows with a rotated part: row = [norm(raw[t, 0:rank]) * w | rot(raw[t, rank:rank+extra])], the rotation by
+ * the token's cos / sin row ([n_tokens, extra/2], b200_rope_angles_amp) in `rot_layout`; stored as `dtype` at the token's
+ * place of the pool, rows of rank + extra. */
+int b200_latent_store_rot(const float* raw, long long ld_raw, const float* w, float eps, void* pool, const int* pages,
+                          int max_pages, int page_rows, const int* slot, const int* pos, int n_tokens, int rank, int extra,
+                          const float* cos, const float* sin, int rot_layout, int dtype, void* stream);
+/* dst[t, h, dst_off + i] = rot(src[t, src_off + h * src_stride + 0:dims])[i] for i < dims: the rotated part of every head's
+ * query placed behind its absorbed part (fp32 to fp32; dst rows of ld_dst floats, heads dst_stride apart) */
+int b200_rotate_part(const float* src, long long ld_src, long long src_off, long long src_stride, float* dst, long long ld_dst,
+                     long long dst_off, long long dst_stride, const float* cos, const float* sin, int rot_layout, int n_tokens,
+                     int heads, int dims, void* stream);
 
 /* Router of a mixture of experts with identity experts: z = h W_r^T (fp32 accumulate; h of h_dtype, W_r fp32
  * [n_out, width]); s = softmax(z) over all n_out outputs; the `top` largest of s + correction are chosen; their weights
@@ -145,6 +181,10 @@ typedef struct b200_rmsnorm_residual_args {
     const float* w; float w_offset, eps;
     void* out; int out_dtype;
     int n_rows, width;
+    /* norm_addend != 0 (layers whose norm sits on the sublayer's OUTPUT): x[t,:] += (y1[t,:] + y_bias[:]) / rms(y1[t,:] +
+       y_bias[:]) * (w_offset + w[:]), then out[t,:] = x[t,:] as out_dtype (what the next sublayer reads; out may be NULL).
+       Only y1 (and y_bias, fp32 [width] or NULL) is added. */
+    int norm_addend; const float* y_bias;
 } b200_rmsnorm_residual_args;
 int b200_rmsnorm_residual(const b200_rmsnorm_residual_args* a, void* stream);
 
@@ -184,6 +224,11 @@ typedef struct b200_qk_prepare_args {
     /* projected values: v_heads > 0 stores proj[t, v_off + g * vdim + :] unchanged (no convolution, norm or rotation) at the
        token's row of v_pool [n_pages*page_rows, v_heads, vdim]; not together with v_from_conv */
     int v_heads, vdim; long long v_off;
+    /* bias: fp32 [ld_proj], added to every column of proj that the launch reads (q, k and the projected values) before
+       anything else. v_cos / v_sin [n_tokens, vdim/2]: the projected values are rotated by their own position over all
+       vdim dimensions (pairs in v_rot_layout) before the store. Both may be NULL. */
+    const float* bias;
+    const float* v_cos; const float* v_sin; int v_rot_layout;
 } b200_qk_prepare_args;
 int b200_qk_prepare(const b200_qk_prepare_args* a, void* stream);
 /* The last taps-1 inputs of every sequence of the step go to their ring places (end[t] = the sequence's length after
@@ -215,6 +260,10 @@ typedef struct b200_paged_attention_args {
        against map m of its key head and weights that head's values). 0 or 1: one map.
        out_f32 != 0: out is fp32 whatever `dtype` (a caller that combines maps or gates in fp32). */
     int chunk, maps, out_f32;
+    /* window > 0: position p only sees the keys j with 0 <= p - j < window (together with chunk: both masks).
+       sigmoid_weights != 0: no softmax; the weight of a visible key is sigmoid(s_j + head_bias[h]) (head_bias fp32 [heads]
+       or NULL), not normalised over the keys: out = sum_j w_j v_j. Not with softcap, denom_bias or maps > 1. */
+    int window, sigmoid_weights; const float* head_bias;
 } b200_paged_attention_args;
 size_t b200_paged_attention_workspace_bytes(int n_tokens, int heads, int vdim);
 int b200_paged_attention(const b200_paged_attention_args* a, void* stream);
@@ -248,6 +297,42 @@ int b200_diff_combine(const float* a, float lambda, float eps, float out_scale, 
 /* out[t, c] = o[t, c] * sigmoid(gate[t, c]) as out_dtype; o fp32 [n_tokens, n], gate fp32 with leading dimension ld_gate */
 int b200_sigmoid_gate(const float* o, const float* gate, long long ld_gate, void* out, int n_tokens, int n, int out_dtype,
                       void* stream);
+
+/* Heads whose values were rotated by their own position: out[t, h, :] = rot(-pos[t])(o[t, h, :]) * sigmoid(gate[t * ld_gate +
+ * h]) as out_dtype. o fp32 [n_tokens, heads, vdim]; cos / sin [n_tokens, vdim/2] of the token's position (the same tables
+ * that rotated the values; the turn back is their conjugate); gate (fp32, one number per head) may be NULL. */
+int b200_unrotate_gate(const float* o, const float* cos, const float* sin, int rot_layout, const float* gate, long long ld_gate,
+                       void* out, int n_tokens, int heads, int vdim, int out_dtype, void* stream);
+
+/* Element-wise gated recurrence whose gate and candidate read only the current token. Per entry (a run of consecutive
+ * tokens of one sequence) and channel c, with z = sigmoid(pre[t, z_off + c] + z_bias[c]), u = pre[t, u_off + c] + u_bias[c]
+ * and the candidate cand = u + 1/2 where u >= 0, sigmoid(u) where u < 0:
+ *   S[c] <- (1 - z) S[c] + z cand;   out[t, c] = S[c] * silu(pre[t, g_off + c])      (as out_dtype)
+ * S fp32 [n_slots, channels], starting from zero when the entry starts at position 0 and left in place for the next
+ * step. pre fp32 [n_tokens, ld_pre]; biases fp32 [channels] or NULL. All arithmetic fp32. Entries longer than a chunk of
+ * tokens run in three launches (chunk summaries, their sequential combination, the chunks again from their true start
+ * states) and need the workspace. */
+typedef struct b200_gated_recurrence_args {
+    const float* pre; long long ld_pre; int z_off, u_off, g_off;
+    const float* z_bias; const float* u_bias;
+    float* state; void* out; int out_dtype;
+    const int* ent_row; const int* ent_len; const int* slot; const int* pos;
+    int n_entries, n_tokens, channels, longest_entry;
+    void* workspace; size_t workspace_bytes;
+} b200_gated_recurrence_args;
+size_t b200_gated_recurrence_workspace_bytes(int n_tokens, int n_entries, int channels);
+int b200_gated_recurrence(const b200_gated_recurrence_args* a, void* stream);
+
+/* out[t,:] = table[ids[t],:] * scale + pair_table[row(t),:] as fp32, row(t) = (prev[t] * mul_prev + ids[t] * mul_cur) mod
+ * buckets (64-bit arithmetic), or row `buckets` (the table's last) where prev[t] < 0: a sequence's first token. pair_table
+ * [buckets + 1, width] may be NULL. Tables of `dtype`; out_cast (may be NULL) receives the same rows as `dtype`: the operand of
+ * a first sublayer that reads the residual stream itself. */
+int b200_embed_pair_hash(const int* ids, const int* prev, const void* table, float scale, const void* pair_table, int buckets,
+                         int mul_prev, int mul_cur, float* out, void* out_cast, int n_tokens, int width, int dtype, void* stream);
+/* v[i] *= f */
+int b200_scale(float* v, size_t n, float f, void* stream);
+/* the clamped GLU of a [gate | up] product computed without the fused epilogue (B200_GG_GLU_CLAMP; gu fp32 [n_rows, 2 n]) */
+int b200_glu_act_clamped(const float* gu, void* out, int n_rows, int n, float limit, int out_dtype, void* stream);
 
 /* Selective scan (a recurrence with input-dependent step sizes and a diagonal transition per channel), in three pieces.
  *

@@ -3,7 +3,10 @@
 // single decoded tokens and mixed batches run through the same launch: every token carries its sequence slot and
 // position, and only sees its own sequence's pages. Two more masks and layouts are arguments: a block mask (a position
 // only sees the keys of its own block of `chunk` positions) and several score maps per head over shared values (`maps`:
-// query unit (h, m) scores against key unit (h / group, m) and weights the values of key head h / group).
+// query unit (h, m) scores against key unit (h / group, m) and weights the values of key head h / group). A sliding window
+// (a position sees itself and the window - 1 positions before it) is a third mask, and the weights can be sigmoids of the
+// score plus a number per head instead of a softmax: then nothing is normalised over the keys, which in the running
+// (maximum, denominator, output) form is a maximum held at 0 and a denominator held at 1.
 //
 //   paged_attn_row_kernel   one CTA per (token, query head), fp32 arithmetic on caches of either dtype: each warp
 //                           takes blocks of 32 keys (a lane scores one key; the weighted value sum runs with a lane per
@@ -30,9 +33,14 @@ struct PA {
     float scale, softcap, denom_bias;
     int splits; float* part;   // row kernel: shares of a context split over gridDim.z CTAs, [token, head, split, 2 + vdim]
     int chunk, maps, out_f32;
+    int window, sigmoid; const float* head_bias;
 };
 // first key that position p sees
-__device__ __forceinline__ int pa_first_key(const PA& a, int p) { return a.chunk > 0 ? (p / a.chunk) * a.chunk : 0; }
+__device__ __forceinline__ int pa_first_key(const PA& a, int p) {
+    const int f = a.chunk > 0 ? (p / a.chunk) * a.chunk : 0;
+    return a.window > 0 ? max(f, p - a.window + 1) : f;
+}
+__device__ __forceinline__ float pa_sigmoid(float v) { return 1.f / (1.f + expf(-v)); }
 template <typename T>
 __device__ __forceinline__ void pa_store(const PA& a, size_t idx, float v) {
     if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = v;
@@ -94,6 +102,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     const int per = ((p - j_lo + a.splits) / a.splits + 31) & ~31;
     const int j_begin = j_lo + blockIdx.z * per, j_end = min(p + 1, j_begin + per);
     if (warp == 0 && blockIdx.z == 0 && a.denom_bias > 0.f) { m = 0.f; l = a.denom_bias; }
+    const float hb = (a.sigmoid && a.head_bias) ? a.head_bias[h / a.maps] : 0.f;
+    if (a.sigmoid) { m = 0.f; l = (warp == 0 && blockIdx.z == 0) ? 1.f : 0.f; }
     for (int j0 = j_begin + warp * 32; j0 < j_end; j0 += kRowWarps * 32) {
         const int j = j0 + lane;
         const bool ok = j < j_end;
@@ -107,10 +117,10 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
         float bm = s;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, d));
-        const float mn = fmaxf(m, bm);
+        const float mn = a.sigmoid ? 0.f : fmaxf(m, bm);
         const float corr = expf(m - mn);   // m = -inf: 0
-        const float pj = ok ? expf(s - mn) : 0.f;
-        float ps = pj;
+        const float pj = !ok ? 0.f : a.sigmoid ? pa_sigmoid(s + hb) : expf(s - mn);
+        float ps = a.sigmoid ? 0.f : pj;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, d);
         l = l * corr + ps;
@@ -187,8 +197,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const bool sink = warp == 0 && blockIdx.z == 0 && a.denom_bias > 0.f;
-        m[r] = sink ? 0.f : -INFINITY;
-        l[r] = sink ? a.denom_bias : 0.f;
+        m[r] = (sink || a.sigmoid) ? 0.f : -INFINITY;
+        l[r] = sink ? a.denom_bias : (a.sigmoid && warp == 0 && blockIdx.z == 0) ? 1.f : 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[r][c][0] = o[r][c][1] = 0.f;
     }
@@ -255,10 +265,11 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
             float bm = sv;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, d));
-            const float mn = fmaxf(m[r], bm);          // finite: the block holds at least one key
+            const float mn = a.sigmoid ? 0.f : fmaxf(m[r], bm);          // finite: the block holds at least one key
             const float corr = expf(m[r] - mn);
-            const float pj = expf(sv - mn);            // a masked key: exp(-inf) = 0
-            float ps = pj;
+            // a masked key: exp(-inf) = 0
+            const float pj = !a.sigmoid ? expf(sv - mn) : sv == -INFINITY ? 0.f : pa_sigmoid(sv + (a.head_bias ? a.head_bias[g * R + r] : 0.f));
+            float ps = a.sigmoid ? 0.f : pj;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, d);
             l[r] = l[r] * corr + ps;
@@ -379,7 +390,7 @@ __device__ __forceinline__ uint32_t pa_pack(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D, int DV, bool BLOCKS>   // dim == D (a multiple of 32), vdim == DV (a multiple of 16); BLOCKS: a.chunk > 0
+template <int D, int DV, bool BLOCKS>   // dim == D (a multiple of 32), vdim == DV (a multiple of 16); BLOCKS: a block mask or a window
 __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel(const PA a) {
     using bf = __nv_bfloat16;
     constexpr int RS = D + 8;                 // row stride in elements: 16-byte aligned, conflict-free fragment loads
@@ -417,8 +428,10 @@ __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel
     float o[DV / 8][4];
 #pragma unroll
     for (int nt = 0; nt < DV / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-    const float m0 = a.denom_bias > 0.f ? 0.f : -1e30f;
-    float m_run[2] = {m0, m0}, l_run[2] = {a.denom_bias, a.denom_bias};
+    const bool sig = a.sigmoid != 0;
+    const float m0 = (a.denom_bias > 0.f || sig) ? 0.f : -1e30f, l0 = sig ? 1.f : a.denom_bias;
+    float m_run[2] = {m0, m0}, l_run[2] = {l0, l0};
+    const float hb = (sig && a.head_bias) ? a.head_bias[h / a.maps] : 0.f;
     const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;
     const float scale_over_cap = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
     const bf* Kp = reinterpret_cast<const bf*>(a.k_pool);
@@ -531,6 +544,12 @@ __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel
                     s[nt][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
+            if (sig) {   // weights that are not normalised over the keys: nothing runs along the row
+#pragma unroll
+                for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] = s[nt][e] == -INFINITY ? 0.f : 1.f / (1.f + __expf(-(s[nt][e] + hb)));
+            } else {
             float alpha[2];
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
@@ -557,6 +576,7 @@ __global__ void __launch_bounds__(128, DV <= 128 ? 3 : 2) paged_attn_tile_kernel
             }
 #pragma unroll
             for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
+            }
 #pragma unroll
             for (int kk = 0; kk < kTileN / 16; ++kk) {
                 uint32_t pf[4];
@@ -601,7 +621,7 @@ static int launch_tile(const PA& a, cudaStream_t s) {
     static unsigned long long done = 0;
     static_assert(DV % D == 0, "a thread brings DV / D value chunks with every key chunk");
     const dim3 grid((a.n_tokens + kTileM - 1) / kTileM, a.heads * a.maps);
-    if (a.chunk > 0) {
+    if (a.chunk > 0 || a.window > 0) {
         static unsigned long long done_b = 0;
         const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D, DV, true>, smem, done_b);
         if (e != cudaSuccess) return (int)e;
@@ -632,13 +652,15 @@ extern "C" size_t b200_paged_attention_workspace_bytes(int n_tokens, int heads, 
 extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* stream) {
     if (!p || !p->q || !p->out || !p->k_pool || !p->v_pool || !p->pages || !p->slot || !p->pos || p->n_tokens < 0 || p->heads < 1 ||
         p->kv_heads < 1 || p->heads % p->kv_heads || p->dim < 1 || p->vdim < 1 || p->page_rows < 1 || p->denom_bias < 0.f ||
-        p->chunk < 0 || p->maps < 0)
+        p->chunk < 0 || p->maps < 0 || p->window < 0)
         return B200_EINVAL;
+    if (p->sigmoid_weights && (p->softcap > 0.f || p->denom_bias > 0.f || p->maps > 1)) return B200_EINVAL;
     const int maps = p->maps > 0 ? p->maps : 1, units = p->heads * maps;
     if (p->vdim > 32 * kMaxVPerLane) return B200_EUNSUPPORTED;
     if (p->n_tokens == 0) return B200_OK;
     PA a{p->q, p->out, p->k_pool, p->v_pool, p->pages, p->max_pages, p->page_rows, p->slot, p->pos, p->n_tokens, p->heads,
-         p->kv_heads, p->dim, p->vdim, p->scale, p->softcap, p->denom_bias, 1, nullptr, p->chunk, maps, p->out_f32};
+         p->kv_heads, p->dim, p->vdim, p->scale, p->softcap, p->denom_bias, 1, nullptr, p->chunk, maps, p->out_f32,
+         p->window, p->sigmoid_weights != 0, p->head_bias};
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = ((size_t)p->dim + (size_t)kRowWarps * p->vdim) * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
@@ -658,7 +680,8 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
                        ((size_t)R * p->dim + (size_t)kRowWarps * R * (32 + p->vdim)) * sizeof(float) <= 48 * 1024;
     const long long ctas = (long long)p->n_tokens * (group ? p->kv_heads * maps : units);
     // few rows with long contexts (decode batches): split every context over several CTAs and merge the shares
-    const int longest_seen = p->chunk > 0 ? std::min(p->longest_context, p->chunk) : p->longest_context;
+    int longest_seen = p->chunk > 0 ? std::min(p->longest_context, p->chunk) : p->longest_context;
+    if (p->window > 0) longest_seen = std::min(longest_seen, p->window);
     if (longest_seen > 256 && p->workspace && (long long)p->n_tokens * units < 2 * sm_count()) {
         int splits = (int)((4ll * sm_count() + ctas - 1) / ctas);
         splits = std::min(std::min(splits, kMaxSplits), (longest_seen + 127) / 128);

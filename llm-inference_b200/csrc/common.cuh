@@ -41,6 +41,12 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// clamped gated unit: g = min(gate, limit), u = clamp(up, -limit, limit); g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float glu_clamp_f(float gate, float up, float limit) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
 // 16-byte packet: the unit every bandwidth kernel moves per thread per access.
 struct __align__(16) Pack16 {
     uint32_t w[4];

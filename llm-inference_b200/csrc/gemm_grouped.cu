@@ -26,6 +26,7 @@ struct GG {
     const int* a_rows; const int* group_off;
     long long lda, ldw, ldc, ld_aux, sA, sW, sC, s_aux;
     int M, N, K, epi;
+    float epi_param;
 };
 
 constexpr int GBM = 64, GBN = 64, GBK = 16;
@@ -35,6 +36,7 @@ __device__ __forceinline__ void gg_store(const GG& g, TC* C, long long row, int 
     if (g.epi == B200_GG_SIGMOID_MUL) v *= 1.f / (1.f + expf(-g.aux[aux_off + row * g.ld_aux + col]));
     else if (g.epi == B200_GG_GLU) v = v / (1.f + expf(-v)) * v2;
     else if (g.epi == B200_GG_GLU_GELU) v = gelu_tanh_f(v) * v2;
+    else if (g.epi == B200_GG_GLU_CLAMP) v = glu_clamp_f(v, v2, g.epi_param);
     else if (g.epi == B200_GG_RELU2) { v = fmaxf(v, 0.f); v *= v; }
     else if (g.epi == B200_GG_BIAS_SOFTPLUS) {
         v += g.aux[aux_off + row * g.ld_aux + col];
@@ -327,7 +329,7 @@ __global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
 
 template <typename TA, typename TW, typename TC>
 static int gg_launch_simt(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
-    if (g.epi == B200_GG_GLU || g.epi == B200_GG_GLU_GELU) {
+    if (g.epi == B200_GG_GLU || g.epi == B200_GG_GLU_GELU || g.epi == B200_GG_GLU_CLAMP) {
         if (!trans_b) return B200_EUNSUPPORTED;
         gemm_grouped_simt_kernel<TA, TW, TC, true, true><<<grid, 256, 0, s>>>(g);
     } else if (trans_b)
@@ -353,7 +355,7 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     const bool vec = g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.sA % 8 == 0 && g.sW % 8 == 0 &&
                      al(g.A, sizeof(TA) * 8) && al(g.W, 16) && (trans_b || g.N % 8 == 0);
     const bool tall = g.M > 64;   // the grid was sized for 64-row tiles (M is the row bound of a group)
-    if (g.epi == B200_GG_GLU || g.epi == B200_GG_GLU_GELU) {
+    if (g.epi == B200_GG_GLU || g.epi == B200_GG_GLU_GELU || g.epi == B200_GG_GLU_CLAMP) {
         if (!trans_b) return B200_EUNSUPPORTED;
         gg_launch_mma_tile<TA, TC, true, true>(g, grid, vec, tall, s);
     } else if (trans_b)
@@ -364,7 +366,7 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
 }
 
 int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, int glu, void* workspace,
-                    size_t workspace_bytes, cudaStream_t s);   // gemm_tcgen05.cu (glu: 0 none, 1 silu, 2 tanh-gelu, 3 no GLU but relu squared)
+                    size_t workspace_bytes, cudaStream_t s, float glu_limit = 0.f);   // gemm_tcgen05.cu (glu: 0 none, 1 silu, 2 tanh-gelu, 3 no GLU but relu squared, 4 clamped)
 size_t gemm_tcgen05_ex_workspace_bytes(int M, int N, int K);
 
 static bool mma_enabled() {
@@ -388,7 +390,8 @@ extern "C" int b200_gemm_grouped(const b200_gemm_grouped_args* p, void* stream) 
     g.A = p->A; g.W = p->W; g.C = p->C; g.aux = p->aux; g.a_rows = p->a_rows; g.group_off = p->group_off;
     g.lda = p->lda; g.ldw = p->ldw; g.ldc = p->ldc; g.ld_aux = p->ld_aux;
     g.sA = p->stride_a; g.sW = p->stride_w; g.sC = p->stride_c; g.s_aux = p->stride_aux;
-    g.M = p->M; g.N = p->N; g.K = p->K; g.epi = p->epi;
+    g.M = p->M; g.N = p->N; g.K = p->K; g.epi = p->epi; g.epi_param = p->epi_param;
+    if (p->epi == B200_GG_GLU_CLAMP && !(p->epi_param > 0.f)) return B200_EINVAL;
     // groups: M is the largest number of rows one group can own (the grid covers it; CTAs beyond a group's rows leave)
     dim3 grid((p->N + GBN - 1) / GBN, (p->M + GBM - 1) / GBM, p->batch);
     if (grid.y > 65535 || grid.z > 65535) return B200_EUNSUPPORTED;
@@ -420,17 +423,27 @@ extern "C" size_t b200_linear_ex_workspace_bytes(int n_tokens, int N, int K) {
 
 extern "C" int b200_linear_ex(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
                               void* workspace, size_t workspace_bytes, void* stream) {
-    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 || (epi != B200_GG_NONE && epi != B200_GG_GLU && epi != B200_GG_GLU_GELU && epi != B200_GG_RELU2)) return B200_EINVAL;
+    if (epi == B200_GG_GLU_CLAMP) return B200_EINVAL;   // needs its limit: b200_linear_ex2
+    return b200_linear_ex2(x, W, y, n_tokens, N, K, in_dtype, out_dtype, epi, 0.f, workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200_linear_ex2(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
+                               float epi_param, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 ||
+        (epi != B200_GG_NONE && epi != B200_GG_GLU && epi != B200_GG_GLU_GELU && epi != B200_GG_RELU2 && epi != B200_GG_GLU_CLAMP))
+        return B200_EINVAL;
+    if (epi == B200_GG_GLU_CLAMP && !(epi_param > 0.f)) return B200_EINVAL;
     if (n_tokens == 0) return B200_OK;
     if (in_dtype == B200_BF16 && (out_dtype == B200_BF16 || out_dtype == B200_F32)) {
-        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, epi == B200_GG_GLU ? 1 : epi == B200_GG_GLU_GELU ? 2 : epi == B200_GG_RELU2 ? 3 : 0, workspace,
-                                       workspace_bytes, (cudaStream_t)stream);
+        const int glu = epi == B200_GG_GLU ? 1 : epi == B200_GG_GLU_GELU ? 2 : epi == B200_GG_RELU2 ? 3 : epi == B200_GG_GLU_CLAMP ? 4 : 0;
+        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, glu, workspace, workspace_bytes,
+                                       (cudaStream_t)stream, epi_param);
         if (rc != B200_EUNSUPPORTED) return rc;
     }
     b200_gemm_grouped_args g{};
     g.A = x; g.W = W; g.C = y;
     g.lda = K; g.ldw = K; g.ldc = N;
-    g.M = n_tokens; g.N = N; g.K = K; g.batch = 1; g.trans_b = 1; g.epi = epi;
+    g.M = n_tokens; g.N = N; g.K = K; g.batch = 1; g.trans_b = 1; g.epi = epi; g.epi_param = epi_param;
     g.a_dtype = in_dtype; g.w_dtype = in_dtype; g.c_dtype = out_dtype;
     return b200_gemm_grouped(&g, stream);
 }

@@ -44,7 +44,8 @@ struct GemmParams {
     int m_tiles, n_tiles, splits, k_blocks;
     int in_bf16;        // operands are bfloat16 instead of fp16 (same tiles, other instruction descriptor)
     int out_kind;       // element type of C: 0 fp16 (rounding points of the reference sequence), 1 bfloat16, 2 fp32
-    int glu_act;        // GLU epilogue: 0 silu, 1 gelu in its tanh form (out_kind 1 / 2 only)
+    int glu_act;        // GLU epilogue: 0 silu, 1 gelu in its tanh form, 2 clamped at glu_limit (out_kind 1 / 2 only)
+    float glu_limit;
     int unary;          // plain epilogue: 0 none, 1 the square of relu on every output (after the split-K sum, if any)
 };
 __device__ __forceinline__ float gemm_unary(float v, int unary) {
@@ -228,7 +229,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     uv = __half2float(__float2half_rn(uv));
                                     f[e] = __half2float(__float2half_rn(gv / (1.f + expf(-gv)))) * uv;
                                 } else
-                                    f[e] = (p.glu_act ? gelu_tanh_f(gv) : gv / (1.f + expf(-gv))) * uv;
+                                    f[e] = p.glu_act == 2 ? glu_clamp_f(gv, uv, p.glu_limit) : (p.glu_act ? gelu_tanh_f(gv) : gv / (1.f + expf(-gv))) * uv;
                             }
                             if (col0 + q * 8 + 8 <= p.rows_b) store8(C, dst + q * 8, f, ok);
                         }
@@ -503,10 +504,11 @@ int gemm_tcgen05_f16(const void* x, const void* W, const void* bias, void* y, in
 
 // The same single-CTA kernel for the model families of b200_serve.h: operands fp16 or bfloat16, output fp16 / bfloat16 /
 // fp32 (out_kind as GemmParams), optionally with the GLU epilogue (glu 1 silu, 2 tanh-gelu: W = [2 N, K], gate rows then up
-// rows, N % 128 == 0) or with the square of relu on every output (glu 3: not a GLU, W = [N, K]).
+// rows, N % 128 == 0; glu 4: the clamped gated unit of common.cuh with its limit) or with the square of relu on every output
+// (glu 3: not a GLU, W = [N, K]).
 // Up to 256 token rows the weights stream through the M axis (swapped, split-K); above, tokens are the M axis.
 int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, int glu, void* workspace,
-                    size_t workspace_bytes, cudaStream_t s) {
+                    size_t workspace_bytes, cudaStream_t s, float glu_limit) {
     auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     if (M < 1 || N < 8 || K < 8 || (K & 7) || !al(x) || !al(W) || !al(y)) return B200_EUNSUPPORTED;
     const char* env = getenv("B200_NO_TCGEN05");
@@ -515,7 +517,7 @@ int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, 
     GemmParams p{};
     p.C = y; p.bias = nullptr; p.K = K; p.ldc = N; p.tokens = M;
     p.k_blocks = (K + kBK - 1) / kBK;
-    p.in_bf16 = in_bf16; p.out_kind = out_kind; p.glu_act = glu == 2;
+    p.in_bf16 = in_bf16; p.out_kind = out_kind; p.glu_act = glu == 2 ? 1 : glu == 4 ? 2 : 0; p.glu_limit = glu_limit;
     p.unary = glu == 3 ? 1 : 0;
     if (glu == 3) glu = 0;
     CUtensorMap ma, mb;

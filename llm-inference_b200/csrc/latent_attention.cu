@@ -5,6 +5,10 @@
 //   row and no value (it only enlarges the denominator).
 // Rows live in a page pool [n_pages, page_rows, rank] addressed through per-sequence page lists (page_pool.h), the
 // same lists for every layer. Scores, softmax and the weighted sum are fp32 whatever the cache dtype.
+// Designs that rotate one key part shared by all heads append it to the cached row ([latent | rotated part],
+// latent_store_rot_kernel) and the head's rotated query part to the absorbed query: the score is still one dot product over
+// the row, and of the weighted sum the caller uses the latent columns. A sliding window (window > 0: position p sees rows
+// p - window < j <= p) bounds the walk from below; without a sink (NULL) the softmax is plain.
 //
 // Kernels:
 //   latent_store_kernel        RMS norm (eps inside the root) of the down-projected row, times weight -> its page slot
@@ -20,6 +24,7 @@
 #include "b200_serve.h"
 #include "common.cuh"
 #include "launch_count.h"
+#include "rotary.cuh"
 
 namespace b200 {
 
@@ -48,12 +53,38 @@ __global__ void __launch_bounds__(128) latent_store_kernel(const float* __restri
     for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = DT<T>::from_f(src[i] * r * w[i]);
 }
 
+// row = [norm(raw[0:rank]) * w | rot(raw[rank:rank+extra])]
+template <typename T>
+__global__ void __launch_bounds__(128) latent_store_rot_kernel(const float* __restrict__ raw, long long ld_raw, const float* __restrict__ w,
+                                                               float eps, T* __restrict__ pool, const int* __restrict__ pages, int max_pages,
+                                                               int page_rows, const int* __restrict__ slot, const int* __restrict__ pos, int rank,
+                                                               int extra, const float* __restrict__ cs, const float* __restrict__ sn, int layout) {
+    __shared__ float red[4];
+    const int t = blockIdx.x;
+    const float* src = raw + (size_t)t * ld_raw;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) q += src[i] * src[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = q;
+    __syncthreads();
+    const float tot = red[0] + red[1] + red[2] + red[3];
+    const float r = 1.0f / sqrtf(tot / (float)rank + eps);
+    const int p = pos[t];
+    const size_t row = (size_t)pages[(size_t)slot[t] * max_pages + p / page_rows] * page_rows + p % page_rows;
+    T* dst = pool + row * (rank + extra);
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = DT<T>::from_f(src[i] * r * w[i]);
+    const int nf = extra / 2;
+    for (int i = threadIdx.x; i < extra; i += blockDim.x)
+        dst[rank + i] = DT<T>::from_f(rotary_component(src + rank, i, 2 * nf, layout, cs + (size_t)t * nf, sn + (size_t)t * nf));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) latent_attn_kernel(const float* __restrict__ qa, float* __restrict__ out,
                                                           const T* __restrict__ pool, const int* __restrict__ pages,
                                                           int max_pages, int page_rows, const int* __restrict__ slot,
                                                           const int* __restrict__ pos, const float* __restrict__ sink,
-                                                          float scale, int heads, int rank) {
+                                                          float scale, int heads, int rank, int window) {
     extern __shared__ float sm[];          // q[rank] | o[4][rank] | m[4] | l[4]
     float* q = sm;
     float* so = sm + rank;
@@ -73,7 +104,8 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const float* __restric
     const int n_keys = pos[t] + 1;
     const int* list = pages + (size_t)slot[t] * max_pages;
     float m = -INFINITY, l = 0.f;
-    for (int j = warp; j < n_keys; j += 4) {
+    const int j_lo = window > 0 ? max(0, n_keys - window) : 0;
+    for (int j = j_lo + warp; j < n_keys; j += 4) {
         const T* c = pool + ((size_t)list[j / page_rows] * page_rows + j % page_rows) * rank;
         float cr[kMaxRankPerLane];
         float d = 0.f;
@@ -100,7 +132,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const float* __restric
     }
     if (lane == 0) { sml[warp] = m; sml[4 + warp] = l; }
     __syncthreads();
-    const float sk = sink[h];
+    const float sk = sink ? sink[h] : -INFINITY;   // no sink: nothing joins the denominator
     float M = sk;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[w]);
@@ -150,7 +182,7 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
                                                                int max_pages, int page_rows, const int* __restrict__ slot,
                                                                const int* __restrict__ pos, const float* __restrict__ sink, float scale,
                                                                int n_tokens, int heads, int rank, int HG, int TQ, int splits,
-                                                               float* __restrict__ part) {
+                                                               float* __restrict__ part, int window) {
     // splits > 1 (blockIdx.z): this CTA walks one share of the key tiles and leaves (m, l, unnormalised O) per row in
     // `part` [token, head, split, 2 + rank]; latent_attn_combine_kernel merges the shares and the sink
     using bf = __nv_bfloat16;
@@ -176,8 +208,10 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
         int cnt = 1;
         while (first + cnt < ntok && slot[t0 + first + cnt] == sl) ++cnt;
         const int all_keys = pos[t0 + first + cnt - 1] + 1;
-        const int per = ((all_keys + kTileKeys - 1) / kTileKeys + splits - 1) / splits * kTileKeys;   // keys per share
-        const int key_lo = blockIdx.z * per, n_keys = min(all_keys, key_lo + per);
+        // the first row of the segment sees the oldest key: whole tiles from there (a half tile stays inside its page)
+        const int seg_lo = window > 0 ? max(0, pos[t0 + first] - window + 1) / kTileKeys * kTileKeys : 0;
+        const int per = ((all_keys - seg_lo + kTileKeys - 1) / kTileKeys + splits - 1) / splits * kTileKeys;   // keys per share
+        const int key_lo = seg_lo + blockIdx.z * per, n_keys = min(all_keys, key_lo + per);
         const int* list = pages + (size_t)sl * max_pages;
         __syncthreads();   // the previous segment's readers are done with the shared state
         if (threadIdx.x < kTileRows) {
@@ -195,8 +229,9 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int r = warp * 4 + i, h = h0 + r % HG;
-            m_run[i] = splits > 1 ? -1e30f : (h < heads ? sink[h] : 0.f);   // shares: the sink joins in the combine
-            l_run[i] = splits > 1 ? 0.f : 1.f;
+            const bool own_sink = splits == 1 && sink != nullptr;           // shares: the sink joins in the combine
+            m_run[i] = !own_sink ? -1e30f : (h < heads ? sink[h] : 0.f);
+            l_run[i] = own_sink ? 1.f : 0.f;
         }
         float o[2][NT][4];
 #pragma unroll
@@ -272,12 +307,13 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
             for (int i = 0; i < 4; ++i) {   // ---- softmax of rows [4 warp, 4 warp + 4): one key per lane
                 const int r = warp * 4 + i, rp = row_pos[r];
                 const int ka = k0 + lane;
-                const float sa = ka <= rp ? (Ss[r * 36 + lane] + Ss[(kTileRows + r) * 36 + lane]) * scale : -INFINITY;
+                const bool seen = ka <= rp && (window <= 0 || ka > rp - window);
+                const float sa = seen ? (Ss[r * 36 + lane] + Ss[(kTileRows + r) * 36 + lane]) * scale : -INFINITY;
                 float mx = sa;
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
                 const float mn = fmaxf(m_run[i], mx);           // finite: m starts at the sink (or at -1e30 in a share)
-                const float pa = ka <= rp ? expf(sa - mn) : 0.f;
+                const float pa = seen ? expf(sa - mn) : 0.f;
                 float sum = pa;
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
@@ -355,7 +391,7 @@ __global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* _
                                                                   const float* __restrict__ sink, int heads, int rank, int splits) {
     const int t = blockIdx.x, h = blockIdx.y;
     const float* p = part + ((size_t)t * heads + h) * splits * (rank + 2);
-    const float sk = sink[h];
+    const float sk = sink ? sink[h] : -INFINITY;
     float M = sk;
     for (int z = 0; z < splits; ++z) M = fmaxf(M, p[(size_t)z * (rank + 2)]);
     float den = expf(sk - M);
@@ -403,11 +439,44 @@ extern "C" size_t b200_latent_attention_workspace_bytes(int n_tokens, int heads,
     return (size_t)n_tokens * heads * kMaxSplits * (rank + 2) * sizeof(float);
 }
 
+extern "C" int b200_latent_store_rot(const float* raw, long long ld_raw, const float* w, float eps, void* pool, const int* pages,
+                                     int max_pages, int page_rows, const int* slot, const int* pos, int n_tokens, int rank, int extra,
+                                     const float* cos, const float* sin, int rot_layout, int dtype, void* stream) {
+    if (!raw || !w || !pool || !pages || !slot || !pos || n_tokens < 0 || rank < 1 || extra < 0 || page_rows < 1) return B200_EINVAL;
+    if (extra > 0 && (!cos || !sin || (rot_layout != B200_ROPE_HALF && rot_layout != B200_ROPE_INTERLEAVED))) return B200_EINVAL;
+    if (n_tokens == 0) return B200_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == B200_BF16)
+        latent_store_rot_kernel<__nv_bfloat16><<<n_tokens, 128, 0, s>>>(raw, ld_raw, w, eps, (__nv_bfloat16*)pool, pages, max_pages, page_rows,
+                                                                       slot, pos, rank, extra, cos, sin, rot_layout);
+    else if (dtype == B200_F32)
+        latent_store_rot_kernel<float><<<n_tokens, 128, 0, s>>>(raw, ld_raw, w, eps, (float*)pool, pages, max_pages, page_rows, slot, pos, rank,
+                                                               extra, cos, sin, rot_layout);
+    else
+        return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
 extern "C" int b200_latent_attention(const float* qa, float* out, const void* pool, const int* pages, int max_pages,
                                      int page_rows, const int* slot, const int* pos, const float* sink, float scale,
                                      int n_tokens, int heads, int rank, int dtype, int longest_entry, int longest_context,
                                      void* workspace, size_t workspace_bytes, void* stream) {
-    if (!qa || !out || !pool || !pages || !slot || !pos || !sink || n_tokens < 0 || heads < 1 || rank < 1) return B200_EINVAL;
+    if (!sink) return B200_EINVAL;
+    b200_latent_attention_args a{qa, out, pool, pages, max_pages, page_rows, slot, pos, sink, scale, n_tokens, heads, rank, 0, dtype,
+                                 longest_entry, longest_context, workspace, workspace_bytes};
+    return b200_latent_attention_ex(&a, stream);
+}
+
+extern "C" int b200_latent_attention_ex(const b200_latent_attention_args* ap, void* stream) {
+    if (!ap) return B200_EINVAL;
+    const float* qa = ap->qa; float* out = ap->out; const void* pool = ap->pool; const int* pages = ap->pages;
+    const int max_pages = ap->max_pages, page_rows = ap->page_rows; const int* slot = ap->slot; const int* pos = ap->pos;
+    const float* sink = ap->sink; const float scale = ap->scale;
+    const int n_tokens = ap->n_tokens, heads = ap->heads, rank = ap->rank, window = ap->window, dtype = ap->dtype, longest_entry = ap->longest_entry;
+    const int longest_context = window > 0 && ap->longest_context > 0 ? std::min(ap->longest_context, window + kTileKeys) : ap->longest_context;
+    void* workspace = ap->workspace; const size_t workspace_bytes = ap->workspace_bytes;
+    if (!qa || !out || !pool || !pages || !slot || !pos || n_tokens < 0 || heads < 1 || rank < 1 || window < 0) return B200_EINVAL;
     if (rank > 32 * kMaxRankPerLane || heads > 65535) return B200_EUNSUPPORTED;
     if (n_tokens == 0) return B200_OK;
     cudaStream_t s = (cudaStream_t)stream;
@@ -435,7 +504,7 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
             static unsigned long long done = 0;
             if (tsm > 48 * 1024 && ensure_max_dynamic_smem((const void*)kern, 200 * 1024, done) != cudaSuccess) return B200_EUNSUPPORTED;
             kern<<<tg, 256, tsm, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows, slot, pos, sink, scale, n_tokens,
-                                      heads, rank, HG, TQ, splits, part);
+                                      heads, rank, HG, TQ, splits, part, window);
             count_launch();
             if (splits > 1) {
                 latent_attn_combine_kernel<<<dim3(n_tokens, heads), 128, 0, s>>>(part, out, sink, heads, rank, splits);
@@ -450,10 +519,10 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
     }
     if (dtype == B200_BF16)
         latent_attn_kernel<__nv_bfloat16><<<grid, 128, smem, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows,
-                                                                 slot, pos, sink, scale, heads, rank);
+                                                                 slot, pos, sink, scale, heads, rank, window);
     else if (dtype == B200_F32)
         latent_attn_kernel<float><<<grid, 128, smem, s>>>(qa, out, (const float*)pool, pages, max_pages, page_rows, slot, pos,
-                                                         sink, scale, heads, rank);
+                                                         sink, scale, heads, rank, window);
     else
         return B200_EINVAL;
     count_launch();

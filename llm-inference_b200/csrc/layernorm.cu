@@ -182,6 +182,47 @@ __global__ void glu_act_kernel(const float* __restrict__ gu, T* __restrict__ out
     out[i] = DT<T>::from_f((gelu ? gelu_tanh_f(g) : g / (1.f + expf(-g))) * u);
 }
 
+template <typename T>
+__global__ void glu_act_clamped_kernel(const float* __restrict__ gu, T* __restrict__ out, int n, size_t total, float limit) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / n, j = i - t * n;
+    out[i] = DT<T>::from_f(glu_clamp_f(gu[t * 2 * n + j], gu[t * 2 * n + n + j], limit));
+}
+
+__global__ void scale_kernel(float* __restrict__ v, size_t n, float f) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) v[i] *= f;
+}
+
+// scaled token row plus the row of a hashed (previous token, token) table; a sequence's first token takes the table's last row
+template <typename T>
+__global__ void embed_pair_hash_kernel(const int* __restrict__ ids, const int* __restrict__ prev, const T* __restrict__ table, float scale,
+                                       const T* __restrict__ pair_table, int buckets, int mul_prev, int mul_cur, float* __restrict__ out,
+                                       T* __restrict__ out_cast, int width) {
+    const int t = blockIdx.x;
+    const T* e = table + (size_t)ids[t] * width;
+    if (!pair_table) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = DT<T>::to_f(e[i]) * scale;
+            out[(size_t)t * width + i] = v;
+            if (out_cast) out_cast[(size_t)t * width + i] = DT<T>::from_f(v);
+        }
+        return;
+    }
+    long long row = buckets;
+    if (prev[t] >= 0) {
+        row = ((long long)prev[t] * mul_prev + (long long)ids[t] * mul_cur) % buckets;
+        if (row < 0) row += buckets;
+    }
+    const T* p = pair_table + (size_t)row * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = DT<T>::to_f(e[i]) * scale + DT<T>::to_f(p[i]);
+        out[(size_t)t * width + i] = v;
+        if (out_cast) out_cast[(size_t)t * width + i] = DT<T>::from_f(v);
+    }
+}
+
 __global__ void softcap_kernel(float* __restrict__ v, size_t n, float cap) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) v[i] = cap * tanhf(v[i] / cap);
@@ -241,6 +282,44 @@ extern "C" int b200_glu_act(const float* gu, void* out, int n_rows, int n, int e
     if (out_dtype == B200_BF16) glu_act_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(gu, (__nv_bfloat16*)out, n, total, epi == B200_GG_GLU_GELU);
     else if (out_dtype == B200_F32) glu_act_kernel<float><<<grid, 256, 0, s>>>(gu, (float*)out, n, total, epi == B200_GG_GLU_GELU);
     else return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_glu_act_clamped(const float* gu, void* out, int n_rows, int n, float limit, int out_dtype, void* stream) {
+    if (!gu || !out || n_rows < 0 || n < 1 || !(limit > 0.f)) return B200_EINVAL;
+    if (n_rows == 0) return B200_OK;
+    const size_t total = (size_t)n_rows * n;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == B200_BF16) glu_act_clamped_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(gu, (__nv_bfloat16*)out, n, total, limit);
+    else if (out_dtype == B200_F32) glu_act_clamped_kernel<float><<<grid, 256, 0, s>>>(gu, (float*)out, n, total, limit);
+    else return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_scale(float* v, size_t n, float f, void* stream) {
+    if (!v) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(v, n, f);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_embed_pair_hash(const int* ids, const int* prev, const void* table, float scale, const void* pair_table, int buckets,
+                                    int mul_prev, int mul_cur, float* out, void* out_cast, int n_tokens, int width, int dtype, void* stream) {
+    if (!ids || !table || !out || n_tokens < 0 || width < 1 || (pair_table && (!prev || buckets < 1))) return B200_EINVAL;
+    if (n_tokens == 0) return B200_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == B200_BF16)
+        embed_pair_hash_kernel<__nv_bfloat16><<<n_tokens, 128, 0, s>>>(ids, prev, (const __nv_bfloat16*)table, scale, (const __nv_bfloat16*)pair_table,
+                                                                      buckets, mul_prev, mul_cur, out, (__nv_bfloat16*)out_cast, width);
+    else if (dtype == B200_F32)
+        embed_pair_hash_kernel<float><<<n_tokens, 128, 0, s>>>(ids, prev, (const float*)table, scale, (const float*)pair_table, buckets, mul_prev,
+                                                              mul_cur, out, (float*)out_cast, width);
+    else
+        return B200_EINVAL;
     count_launch();
     return (int)cudaGetLastError();
 }

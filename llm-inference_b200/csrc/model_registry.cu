@@ -48,6 +48,7 @@ int SequenceBatch::init(int max_tokens, int page_rows, int slots, int max_pos, s
     const cudaError_t e = pool.init(n_pages, page_rows, slots, per_slot);
     if (e != cudaSuccess) { err = std::string("page pool: ") + cudaGetErrorString(e); return (int)e; }
     length.assign(slots, 0);
+    last_id.assign(slots, -1);
     if (cudaEventCreateWithFlags(&copied_, cudaEventDisableTiming) != cudaSuccess) { err = "cudaEventCreate"; return B200_EINVAL; }
     return B200_OK;
 }
@@ -103,6 +104,7 @@ int SequenceBatch::begin_step(const std::vector<StepEntry>& entries, cudaStream_
     int* end = host_ + 5 * (size_t)cap_;
     int* ent_row = host_ + 6 * (size_t)cap_;
     int* ent_len = host_ + 7 * (size_t)cap_;
+    int* prev = host_ + 8 * (size_t)cap_;
     int t = 0, w = 0, ne = 0;
     for (const StepEntry& en : entries) {
         for (int k = 0; k < en.n_want; ++k) rows[w++] = t + en.want[k];
@@ -114,7 +116,9 @@ int SequenceBatch::begin_step(const std::vector<StepEntry>& entries, cudaStream_
             pos[t] = length[en.slot] + i;
             start[t] = length[en.slot];
             end[t] = length[en.slot] + en.n_tokens;
+            prev[t] = i > 0 ? en.tokens[i - 1] : length[en.slot] > 0 ? last_id[en.slot] : -1;
         }
+        last_id[en.slot] = en.tokens[en.n_tokens - 1];
         length[en.slot] += en.n_tokens;
     }
     n_tokens = total;
@@ -131,6 +135,7 @@ int SequenceBatch::release(int slot) {
     if (slot < 0 || slot >= n_slots) return B200_EINVAL;
     pool.release(slot);
     length[slot] = 0;
+    last_id[slot] = -1;
     return B200_OK;
 }
 
@@ -202,7 +207,7 @@ int StepRunner::ensure_logits_host(int W) {
     return B200_OK;
 }
 
-int StepRunner::gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi) {
+int StepRunner::gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi, float epi_param) {
     const size_t need = b200_linear_ex_workspace_bytes(M, N, K);
     if (need > ws_bytes_ && !capturing_) {
         cudaStreamSynchronize(stream_);
@@ -212,7 +217,7 @@ int StepRunner::gemm(const void* A, const void* W, void* C, int c_dt, int M, int
         ws_bytes_ = 0;
         if (cudaMalloc(&ws_, need) == cudaSuccess) ws_bytes_ = need;   // without it the call runs with a single split
     }
-    return b200_linear_ex(A, W, C, M, N, K, dtype_, c_dt, epi, ws_, ws_bytes_, stream_);
+    return b200_linear_ex2(A, W, C, M, N, K, dtype_, c_dt, epi, epi_param, ws_, ws_bytes_, stream_);
 }
 
 int StepRunner::step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) {

@@ -32,8 +32,9 @@ struct ModelDir {
 // Sequence slots over one PagePool, plus the device tables of a step: for token t of the packed batch its id, slot and
 // position, and for every wanted place its row in the batch; for layers that carry state from token to token also the
 // position at which the token's sequence starts in this step and its length after it (what is older than the step comes
-// from carried state), and per entry its first batch row and its token count. Filled on the host (pinned), uploaded with
-// one copy.
+// from carried state), and per entry its first batch row and its token count; for embeddings that read a pair of tokens,
+// the id of the token before it in its sequence (-1 for a sequence's first token; the last id of every slot is kept from
+// step to step). Filled on the host (pinned), uploaded with one copy.
 class SequenceBatch {
 public:
     ~SequenceBatch();
@@ -47,6 +48,7 @@ public:
     PagePool pool;
     int n_slots = 0, max_positions = 0;
     std::vector<int> length;      // tokens cached per slot
+    std::vector<int> last_id;     // the slot's newest token (what the next step's first token follows)
     // the step prepared by begin_step
     int n_tokens = 0, n_want = 0;
     const int* d_ids() const { return dev_; }
@@ -57,11 +59,12 @@ public:
     const int* d_end() const { return dev_ + 5 * (size_t)cap_; }       // per token: its sequence's length after the step
     const int* d_ent_row() const { return dev_ + 6 * (size_t)cap_; }   // per entry: first row in the batch
     const int* d_ent_len() const { return dev_ + 7 * (size_t)cap_; }   // per entry: tokens
+    const int* d_prev() const { return dev_ + 8 * (size_t)cap_; }      // per token: id of the token before it, -1 at position 0
     int n_entries = 0;
 
 private:
     int ensure_capacity(int tokens);
-    static constexpr int kTables = 8;
+    static constexpr int kTables = 9;
     int* host_ = nullptr;   // pinned [kTables, cap]
     int* dev_ = nullptr;
     int cap_ = 0;
@@ -151,7 +154,7 @@ protected:
     size_t esz() const { return dtype_ == B200_BF16 ? 2 : 4; }
     void* dalloc(size_t bytes);   // device memory owned until the model closes
     // y[M, N] = A[M, K] W[N, K]^T, contiguous; A and W of the serving dtype: the tcgen05 GEMM when it fits, else the grouped one
-    int gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi = B200_GG_NONE);
+    int gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi = B200_GG_NONE, float epi_param = 0.f);
     // the host buffer of the logits follows the largest number of wanted places (called from ensure_scratch)
     int ensure_logits_host(int W);
     void buffers_moved() { ++buffers_epoch_; }   // a buffer that captured launches point into was reallocated

@@ -2,6 +2,8 @@
 // rows of routed experts, a vector shared by all rows) fused with the RMS norm of whatever reads the residual next, so a
 // sublayer boundary is one launch. One CTA per row; the new row stays in shared memory between the sum of squares and
 // the output. With a row list the kernel only norms the listed rows (the final norm before the vocabulary projection).
+// Layers whose norm sits on the sublayer's OUTPUT take the other order (norm_addend): the sublayer's row (plus a bias) is
+// normed, added to the residual, and the new residual row leaves in the serving dtype for the next sublayer to read.
 #include "b200_serve.h"
 #include "common.cuh"
 #include "launch_count.h"
@@ -128,6 +130,70 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_residual_reg_kernel(const RnA
     }
 }
 
+// x += norm(y1 + y_bias) * (w_offset + w); out = x. Rows of at most kRnPer values per thread live in registers (REG), longer
+// ones in shared memory.
+template <typename T, int THREADS, bool REG>
+__global__ void __launch_bounds__(THREADS) rmsnorm_addend_kernel(const RnArgs a, const float* __restrict__ y_bias) {
+    extern __shared__ float rn_row[];
+    __shared__ float red[THREADS / 32];
+    const int i = blockIdx.x, width = a.width;
+    const size_t src = (size_t)i * width;
+    float v[kRnPer], xv[kRnPer], wv[kRnPer];
+    float ss = 0.f;
+    if (REG) {
+#pragma unroll
+        for (int k = 0; k < kRnPer; ++k) {
+            const int c = threadIdx.x + THREADS * k;
+            const bool in = c < width;
+            v[k] = in ? a.y1[src + c] + (y_bias ? y_bias[c] : 0.f) : 0.f;
+            xv[k] = in ? a.x[src + c] : 0.f;
+            wv[k] = in ? a.w[c] : 0.f;
+            ss += v[k] * v[k];
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += THREADS) {
+            const float y = a.y1[src + c] + (y_bias ? y_bias[c] : 0.f);
+            rn_row[c] = y;
+            ss += y * y;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < THREADS / 32; ++k) tot += red[k];   // the same order in every thread
+    const float rinv = 1.0f / sqrtf(tot / (float)width + a.eps);
+    T* out = a.out ? reinterpret_cast<T*>(a.out) + src : nullptr;
+    if (REG) {
+#pragma unroll
+        for (int k = 0; k < kRnPer; ++k) {
+            const int c = threadIdx.x + THREADS * k;
+            if (c >= width) continue;
+            const float nx = xv[k] + v[k] * rinv * (a.w_offset + wv[k]);
+            a.x[src + c] = nx;
+            if (out) out[c] = DT<T>::from_f(nx);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += THREADS) {
+            const float nx = a.x[src + c] + rn_row[c] * rinv * (a.w_offset + a.w[c]);
+            a.x[src + c] = nx;
+            if (out) out[c] = DT<T>::from_f(nx);
+        }
+    }
+}
+
+template <typename T>
+static void launch_addend(const RnArgs& a, const float* y_bias, int n_rows, size_t smem, cudaStream_t s) {
+    if (a.width <= 256 * kRnPer) rmsnorm_addend_kernel<T, 256, true><<<n_rows, 256, 0, s>>>(a, y_bias);
+    else if (a.width <= 1024 * kRnPer) rmsnorm_addend_kernel<T, 1024, true><<<n_rows, 1024, 0, s>>>(a, y_bias);
+    else {
+        static unsigned long long done = 0;
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)rmsnorm_addend_kernel<T, kRnThreads, false>, 200 * 1024, done);
+        rmsnorm_addend_kernel<T, kRnThreads, false><<<n_rows, kRnThreads, smem, s>>>(a, y_bias);
+    }
+}
+
 template <typename T>
 static void launch_rn(const RnArgs& a, int n_rows, size_t smem, cudaStream_t s) {
     if (a.width <= 256 * kRnPer) rmsnorm_residual_reg_kernel<T, 256><<<n_rows, 256, 0, s>>>(a);
@@ -145,7 +211,7 @@ using namespace b200;
 
 extern "C" int b200_rmsnorm_residual(const b200_rmsnorm_residual_args* p, void* stream) {
     if (!p || !p->x || p->n_rows < 0 || p->width < 1) return B200_EINVAL;
-    if (p->w && !p->out) return B200_EINVAL;
+    if (p->w && !p->out && !p->norm_addend) return B200_EINVAL;
     if (p->expert_out && (!p->dest || !p->weight || p->top < 1)) return B200_EINVAL;
     if (p->expert_out && p->top > kRnMaxTop) return B200_EUNSUPPORTED;
     if (p->rows && (p->y1 || p->y2 || p->expert_out || p->bcast)) return B200_EINVAL;
@@ -155,6 +221,14 @@ extern "C" int b200_rmsnorm_residual(const b200_rmsnorm_residual_args* p, void* 
     RnArgs a{p->x, p->y1, p->s1, p->y2, p->s2, p->expert_out, p->dest, p->weight, p->top, p->bcast, p->rows, p->w, p->w_offset, p->eps,
              p->out, p->width};
     cudaStream_t s = (cudaStream_t)stream;
+    if (p->norm_addend) {
+        if (!p->y1 || !p->w || p->y2 || p->expert_out || p->bcast || p->rows) return B200_EINVAL;
+        if (p->out_dtype == B200_BF16 || !p->out) launch_addend<__nv_bfloat16>(a, p->y_bias, p->n_rows, smem, s);
+        else if (p->out_dtype == B200_F32) launch_addend<float>(a, p->y_bias, p->n_rows, smem, s);
+        else return B200_EINVAL;
+        count_launch();
+        return (int)cudaGetLastError();
+    }
     if (p->out_dtype == B200_BF16 || !p->w) launch_rn<__nv_bfloat16>(a, p->n_rows, smem, s);
     else if (p->out_dtype == B200_F32) launch_rn<float>(a, p->n_rows, smem, s);
     else return B200_EINVAL;

@@ -33,6 +33,8 @@ struct QkPrep {
     const int* slot; const int* pos; const int* start;
     int heads, kv_heads, dim;
     int v_heads, vdim; long long v_off;
+    const float* bias; const float* v_cos; const float* v_sin; int v_layout;
+    int vals_per_warp;   // floats of shared memory per warp: max(dim, vdim)
 };
 
 // One warp per (token, head unit): units [0, heads) are query heads, [heads, heads + kv_heads) key heads; a lane owns the
@@ -45,14 +47,23 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, dim = a.dim;
     const int unit = blockIdx.x * kPrepWarps + warp, per_token = a.heads + a.kv_heads;
     if (unit >= n_units) return;
-    float* vals = prep_sm + warp * dim;   // the normed head before rotation
+    float* vals = prep_sm + warp * a.vals_per_warp;   // the normed head before rotation
     const int t = unit / (per_token + a.v_heads), u = unit % (per_token + a.v_heads);
-    if (u >= per_token) {   // a projected value head: copied to its cache row as it is
+    if (u >= per_token) {   // a projected value head: to its cache row, with its bias and turned by its own position if asked
         const int g = u - per_token, pv = a.pos[t];
         const size_t vrow = ((size_t)a.pages[(size_t)a.slot[t] * a.max_pages + pv / a.page_rows] * a.page_rows + pv % a.page_rows) * a.v_heads + g;
-        const float* src = a.proj + (size_t)t * a.ld_proj + a.v_off + (size_t)g * a.vdim;
+        const size_t col0 = (size_t)a.v_off + (size_t)g * a.vdim;
+        const float* src = a.proj + (size_t)t * a.ld_proj + col0;
         T* vd = reinterpret_cast<T*>(a.v_pool) + vrow * a.vdim;
-        for (int i = lane; i < a.vdim; i += 32) vd[i] = DT<T>::from_f(src[i]);
+        if (!a.v_cos) {
+            for (int i = lane; i < a.vdim; i += 32) vd[i] = DT<T>::from_f(src[i] + (a.bias ? a.bias[col0 + i] : 0.f));
+            return;
+        }
+        for (int i = lane; i < a.vdim; i += 32) vals[i] = src[i] + (a.bias ? a.bias[col0 + i] : 0.f);
+        __syncwarp();
+        const int vf = a.vdim / 2;
+        for (int i = lane; i < a.vdim; i += 32)
+            vd[i] = DT<T>::from_f(rotary_component(vals, i, 2 * vf, a.v_layout, a.v_cos + (size_t)t * vf, a.v_sin + (size_t)t * vf));
         return;
     }
     const bool is_k = u >= a.heads;
@@ -126,7 +137,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
             // a one-token entry: nobody else reads this sequence's ring in this launch, and this lane has read its own places
             if (a.ring_out && taps > 1) a.ring_out[((size_t)b * (taps - 1) + p % (taps - 1)) * channels + c] = a.proj[(size_t)t * a.ld_proj + c];
         } else
-            y = a.proj[(size_t)t * a.ld_proj + c];
+            y = a.proj[(size_t)t * a.ld_proj + c] + (a.bias ? a.bias[c] : 0.f);
         if (is_k && a.v_from_conv) reinterpret_cast<T*>(a.v_pool)[cache_row * dim + i] = DT<T>::from_f(y);
         vals[i] = y;
         ss += y * y;
@@ -188,6 +199,19 @@ __global__ void __launch_bounds__(256) qk_rotate_store_kernel(const QkPrep a, lo
     }
 }
 
+// the rotated part of every head's query, placed behind the head's absorbed part: a thread per (token, head, dimension)
+__global__ void rotate_part_kernel(const float* __restrict__ src, long long ld_src, long long src_off, long long src_stride,
+                                   float* __restrict__ dst, long long ld_dst, long long dst_off, long long dst_stride,
+                                   const float* __restrict__ cs, const float* __restrict__ sn, int layout, int heads, int dims, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = (int)(idx % dims), h = (int)((idx / dims) % heads);
+    const size_t t = idx / ((size_t)dims * heads);
+    const int nf = dims / 2;
+    dst[t * ld_dst + dst_off + h * dst_stride + i] =
+        rotary_component(src + t * ld_src + src_off + h * src_stride, i, 2 * nf, layout, cs + t * nf, sn + t * nf);
+}
+
 __global__ void conv_state_update_kernel(const float* __restrict__ proj, long long ld_proj, float* __restrict__ state,
                                          const int* __restrict__ slot, const int* __restrict__ pos, const int* __restrict__ end,
                                          int channels, int taps) {
@@ -224,15 +248,20 @@ extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
     if (p->v_heads < 0 || (p->v_heads > 0 && (!p->v_pool || p->vdim < 1 || p->v_from_conv || p->v_off < 0))) return B200_EINVAL;
     if (p->rot_dims < 0 || (p->rot_dims & 1) || p->rot_dims > p->dim || (p->rot_dims && (!p->cos || !p->sin))) return B200_EINVAL;
     if (p->rot_layout != B200_ROPE_HALF && p->rot_layout != B200_ROPE_INTERLEAVED) return B200_EINVAL;
+    if (p->bias && p->conv_w) return B200_EINVAL;   // carried convolution inputs are raw projections
+    if ((p->v_cos || p->v_sin) && (!p->v_cos || !p->v_sin || p->v_heads < 1 ||
+                                   (p->v_rot_layout != B200_ROPE_HALF && p->v_rot_layout != B200_ROPE_INTERLEAVED)))
+        return B200_EINVAL;
     if (p->n_tokens == 0) return B200_OK;
     QkPrep a{p->proj, p->ld_proj, p->conv_w, p->taps, p->conv_state, p->q_norm, p->k_norm, p->eps, p->cos, p->sin, p->rot_dims,
              p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->update_state_inline ? const_cast<float*>(p->conv_state) : nullptr, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
-             p->start, p->heads, p->kv_heads, p->dim, p->v_heads, p->vdim, p->v_off};
+             p->start, p->heads, p->kv_heads, p->dim, p->v_heads, p->vdim, p->v_off, p->bias, p->v_cos, p->v_sin, p->v_rot_layout,
+             p->v_heads > 0 && p->vdim > p->dim ? p->vdim : p->dim};
     if (a.conv_w && a.taps == 1) a.conv_state = a.proj;   // never read: every input of a one-tap filter is the token's own
     cudaStream_t s = (cudaStream_t)stream;
     {   // rotation and scatters only, everything in whole groups of four: the vector kernel
         auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
-        const bool plain = !p->conv_w && !p->q_norm && !p->k_norm && p->rot_layout == B200_ROPE_HALF && p->dim % 4 == 0 && p->rot_dims % 8 == 0 &&
+        const bool plain = !p->conv_w && !p->q_norm && !p->k_norm && !p->bias && !p->v_cos && p->rot_layout == B200_ROPE_HALF && p->dim % 4 == 0 && p->rot_dims % 8 == 0 &&
                            p->ld_proj % 4 == 0 && al16(p->proj) && al16(p->q_out) && al16(p->k_pool) &&
                            (p->v_heads == 0 || (p->vdim % 4 == 0 && p->v_off % 4 == 0 && al16(p->v_pool))) &&
                            (p->dtype == B200_BF16 || p->dtype == B200_F32);
@@ -249,11 +278,24 @@ extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
     const long long units = (long long)p->n_tokens * (p->heads + p->kv_heads + p->v_heads);
     if (units > 0x7fffffffll) return B200_EUNSUPPORTED;
     const unsigned grid = (unsigned)((units + kPrepWarps - 1) / kPrepWarps);
-    const size_t smem = (size_t)kPrepWarps * p->dim * sizeof(float);
+    const size_t smem = (size_t)kPrepWarps * a.vals_per_warp * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
     if (p->dtype == B200_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, kPrepWarps * 32, smem, s>>>(a, (int)units);
     else if (p->dtype == B200_F32) qk_prepare_kernel<float><<<grid, kPrepWarps * 32, smem, s>>>(a, (int)units);
     else return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_rotate_part(const float* src, long long ld_src, long long src_off, long long src_stride, float* dst, long long ld_dst,
+                                long long dst_off, long long dst_stride, const float* cos, const float* sin, int rot_layout, int n_tokens,
+                                int heads, int dims, void* stream) {
+    if (!src || !dst || !cos || !sin || n_tokens < 0 || heads < 1 || dims < 1) return B200_EINVAL;
+    if (rot_layout != B200_ROPE_HALF && rot_layout != B200_ROPE_INTERLEAVED) return B200_EINVAL;
+    if (n_tokens == 0) return B200_OK;
+    const size_t total = (size_t)n_tokens * heads * dims;
+    rotate_part_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(src, ld_src, src_off, src_stride, dst, ld_dst, dst_off,
+                                                                                         dst_stride, cos, sin, rot_layout, heads, dims, total);
     count_launch();
     return (int)cudaGetLastError();
 }

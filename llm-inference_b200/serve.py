@@ -8,7 +8,7 @@ import numpy as np
 from . import capi
 
 F32, BF16 = 0, 2
-GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU, GG_RELU2, GG_BIAS_SOFTPLUS = 0, 1, 2, 3, 4, 5
+GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU, GG_RELU2, GG_BIAS_SOFTPLUS, GG_GLU_CLAMP = 0, 1, 2, 3, 4, 5, 6
 ROPE_HALF, ROPE_INTERLEAVED = 0, 1
 _vp, _i, _f, _sz, _ll = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_longlong
 
@@ -19,7 +19,7 @@ class GemmGroupedArgs(C.Structure):
                 ("lda", _ll), ("ldw", _ll), ("ldc", _ll), ("ld_aux", _ll),
                 ("stride_a", _ll), ("stride_w", _ll), ("stride_c", _ll), ("stride_aux", _ll),
                 ("M", _i), ("N", _i), ("K", _i), ("batch", _i), ("trans_b", _i), ("epi", _i),
-                ("a_dtype", _i), ("w_dtype", _i), ("c_dtype", _i)]
+                ("a_dtype", _i), ("w_dtype", _i), ("c_dtype", _i), ("epi_param", _f)]
 
 
 class QkPrepareArgs(C.Structure):
@@ -29,7 +29,8 @@ class QkPrepareArgs(C.Structure):
                 ("q_out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("v_from_conv", _i),
                 ("pages", _vp), ("max_pages", _i), ("page_rows", _i), ("slot", _vp), ("pos", _vp), ("start", _vp),
                 ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("dtype", _i), ("update_state_inline", _i),
-                ("v_heads", _i), ("vdim", _i), ("v_off", _ll)]
+                ("v_heads", _i), ("vdim", _i), ("v_off", _ll),
+                ("bias", _vp), ("v_cos", _vp), ("v_sin", _vp), ("v_rot_layout", _i)]
 
 
 class PagedAttentionArgs(C.Structure):
@@ -38,14 +39,16 @@ class PagedAttentionArgs(C.Structure):
                 ("slot", _vp), ("pos", _vp), ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("vdim", _i),
                 ("scale", _f), ("softcap", _f), ("denom_bias", _f), ("dtype", _i), ("longest_entry", _i),
                 ("longest_context", _i), ("workspace", _vp), ("workspace_bytes", _sz),
-                ("chunk", _i), ("maps", _i), ("out_f32", _i)]
+                ("chunk", _i), ("maps", _i), ("out_f32", _i),
+                ("window", _i), ("sigmoid_weights", _i), ("head_bias", _vp)]
 
 
 class RmsnormResidualArgs(C.Structure):
     """mirror of ``b200_rmsnorm_residual_args``"""
     _fields_ = [("x", _vp), ("y1", _vp), ("s1", _f), ("y2", _vp), ("s2", _f),
                 ("expert_out", _vp), ("dest", _vp), ("weight", _vp), ("top", _i), ("bcast", _vp), ("rows", _vp),
-                ("w", _vp), ("w_offset", _f), ("eps", _f), ("out", _vp), ("out_dtype", _i), ("n_rows", _i), ("width", _i)]
+                ("w", _vp), ("w_offset", _f), ("eps", _f), ("out", _vp), ("out_dtype", _i), ("n_rows", _i), ("width", _i),
+                ("norm_addend", _i), ("y_bias", _vp)]
 
 
 class ConvActArgs(C.Structure):
@@ -70,6 +73,22 @@ class RetentionArgs(C.Structure):
                 ("cos", _vp), ("sin", _vp), ("rot_dims", _i), ("rot_layout", _i), ("decay", _vp), ("k_scale", _f),
                 ("state", _vp), ("out", _vp), ("ent_row", _vp), ("ent_len", _vp), ("slot", _vp), ("pos", _vp),
                 ("n_entries", _i), ("n_tokens", _i), ("heads", _i), ("dim", _i), ("vdim", _i), ("longest_entry", _i),
+                ("workspace", _vp), ("workspace_bytes", _sz)]
+
+
+class LatentAttentionArgs(C.Structure):
+    """mirror of ``b200_latent_attention_args``"""
+    _fields_ = [("qa", _vp), ("out", _vp), ("pool", _vp), ("pages", _vp), ("max_pages", _i), ("page_rows", _i),
+                ("slot", _vp), ("pos", _vp), ("sink", _vp), ("scale", _f), ("n_tokens", _i), ("heads", _i), ("rank", _i),
+                ("window", _i), ("dtype", _i), ("longest_entry", _i), ("longest_context", _i),
+                ("workspace", _vp), ("workspace_bytes", _sz)]
+
+
+class GatedRecurrenceArgs(C.Structure):
+    """mirror of ``b200_gated_recurrence_args``"""
+    _fields_ = [("pre", _vp), ("ld_pre", _ll), ("z_off", _i), ("u_off", _i), ("g_off", _i), ("z_bias", _vp), ("u_bias", _vp),
+                ("state", _vp), ("out", _vp), ("out_dtype", _i), ("ent_row", _vp), ("ent_len", _vp), ("slot", _vp), ("pos", _vp),
+                ("n_entries", _i), ("n_tokens", _i), ("channels", _i), ("longest_entry", _i),
                 ("workspace", _vp), ("workspace_bytes", _sz)]
 
 
@@ -112,6 +131,16 @@ SERVE_PROTOTYPES = {
     "b200_conv_act": (_i, [C.POINTER(ConvActArgs), _vp]),
     "b200_selective_scan_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "b200_selective_scan": (_i, [C.POINTER(SelectiveScanArgs), _vp]),
+    "b200_linear_ex2": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "b200_latent_attention_ex": (_i, [C.POINTER(LatentAttentionArgs), _vp]),
+    "b200_latent_store_rot": (_i, [_vp, _ll, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
+    "b200_rotate_part": (_i, [_vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "b200_unrotate_gate": (_i, [_vp, _vp, _vp, _i, _vp, _ll, _vp, _i, _i, _i, _i, _vp]),
+    "b200_gated_recurrence_workspace_bytes": (_sz, [_i, _i, _i]),
+    "b200_gated_recurrence": (_i, [C.POINTER(GatedRecurrenceArgs), _vp]),
+    "b200_embed_pair_hash": (_i, [_vp, _vp, _vp, _f, _vp, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_scale": (_i, [_vp, _sz, _f, _vp]),
+    "b200_glu_act_clamped": (_i, [_vp, _vp, _i, _i, _f, _i, _vp]),
     "b200_serve_last_error": (C.c_char_p, []),
     "b200_model_families": (C.c_char_p, []),
     "b200_model_open": (_vp, [C.c_char_p, C.POINTER(ModelOptions)]),
