@@ -251,7 +251,7 @@ def random_model(seed, width, vocab, layers, buckets=53, mul_prev=7, mul_cur=3, 
             w[pre + "norm2"] = 1 + rnd(width, s=0.1)
             w[pre + "mlp.gate"], w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(f, width, s=2.0 / math.sqrt(width)), rnd(f, width, s=2.0 / math.sqrt(width)), rnd(width, f)
         cfg["layers"].append(dict(type=sp["type"], mixer=mx, mlp=ml))
-    return cfg, w
+    return cfg, {k: v.to(torch.bfloat16).to(DT) for k, v in w.items()}     # weights around one are sums: rounded once more
 
 
 def write_model(folder, cfg, w):

@@ -19,7 +19,7 @@ def S(pkg):
 
 def test_registry_lists_the_families(S):
     fams = S.lib().b200_model_families().decode().split(",")
-    assert "Nekodra" in fams and "Musilorn" in fams and "Tomalix" in fams and "llama" in fams
+    assert "Nekodra" in fams and "Musilorn" in fams and "Tomalix" in fams and "Sakevik" in fams and "llama" in fams
 
 
 def test_unknown_architecture_and_broken_config(S, tmp_path):
@@ -177,3 +177,96 @@ def test_written_checkpoint_has_the_documented_layout(tmp_path):
     assert header["l0.mix.q"]["shape"] == [48, 64] and header["l0.mix.q"]["dtype"] == "BF16"
     assert "l1.mix.dkv" not in header and "l0.mix.dkv" in header    # the second layer reads the first one's rows
     assert json.loads((tmp_path / "config.json").read_text())["layers"][1]["mixer"]["kv_from"] == 0
+
+
+def test_sakevik_configuration_errors_end_before_any_cuda_call(S, tmp_path):
+    head = '{"architecture": "Sakevik", "width": 8, "vocab": 5, "norm": {"eps": 1e-5}, '
+    (tmp_path / "config.json").write_text(head + '"layers": []}')
+    with pytest.raises(RuntimeError, match="required"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "retention", "mixer": {}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="not part of this family"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "mingru", "mixer": {"width": 4}, "mlp": {"kind": "moe"}}]}')
+    with pytest.raises(RuntimeError, match="feed-forward kind"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "mingru", "mixer": {"width": 4}, "mlp": {"kind": "dense", "ff": 8}}]}')
+    with pytest.raises(RuntimeError, match="limit"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "attention", "mixer": {"heads": 3, "kv_heads": 2, "dim": 4, "vdim": 4, '
+                                          '"scale": 0.5}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="multiple of kv_heads"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"layers": [{"type": "latent_attention", "mixer": {"heads": 2, "dim": 4, "vdim": 4, "kv_rank": 6, '
+                                          '"rot_dim": 4, "rot": {"base": 100.0, "dims": 2}, "scale": 0.5}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="rot_dim"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text(head + '"embedding": {"scale": 1.0, "bigram": {"buckets": 0, "mul_prev": 1, "mul_cur": 1}}, '
+                                          '"layers": [{"type": "mingru", "mixer": {"width": 4}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="buckets"):
+        S.Model(tmp_path)
+
+
+def test_sakevik_oracle_pieces_agree_with_closed_forms():
+    """the plain implementation of the fourth family: the norm, the pair rows, both rotation layouts and their inverse, the
+    ramp, the window, the recurrence against its unrolled sum, sigmoid weights that do not sum to one, the clamped unit"""
+    import sakevik_oracle as K
+    g = torch.Generator().manual_seed(3)
+    D = torch.float64
+    x = torch.randn(4, 6, generator=g, dtype=D)
+    assert torch.allclose(K.rms_norm(x, torch.full((6,), 2.0, dtype=D), 0.0), 2 * x / x.pow(2).mean(-1, keepdim=True).sqrt())
+    cfg = dict(embedding=dict(scale=3.0, bigram=dict(buckets=5, mul_prev=7, mul_cur=3)))
+    W = dict(embed=torch.randn(9, 2, generator=g, dtype=D), bigram=torch.randn(6, 2, generator=g, dtype=D))
+    e = K.embed(cfg, W, [4, 8, 8])
+    assert torch.allclose(e[0], 3 * W["embed"][4] + W["bigram"][5]) and torch.allclose(e[1], 3 * W["embed"][8] + W["bigram"][(4 * 7 + 8 * 3) % 5])
+    assert torch.allclose(e[2], 3 * W["embed"][8] + W["bigram"][(8 * 7 + 8 * 3) % 5])
+    q = torch.randn(5, 2, 6, generator=g, dtype=D)
+    ang = K.pair_angles(5, 2, 100.0, 4)
+    a = 3 * 100.0 ** (-2 / 4)
+    r = K.turn(q, ang, "half")
+    assert torch.equal(r[..., 4:], q[..., 4:]) and torch.equal(r[0], q[0])
+    assert torch.allclose(r[3, 1, 1], q[3, 1, 1] * math.cos(a) - q[3, 1, 3] * math.sin(a))
+    assert torch.allclose(r[3, 1, 3], q[3, 1, 3] * math.cos(a) + q[3, 1, 1] * math.sin(a))
+    ri = K.turn(q, ang, "interleaved", 1.5)
+    assert torch.allclose(ri[3, 0, 2], 1.5 * (q[3, 0, 2] * math.cos(a) - q[3, 0, 3] * math.sin(a)))
+    assert torch.allclose(ri[3, 0, 3], 1.5 * (q[3, 0, 3] * math.cos(a) + q[3, 0, 2] * math.sin(a)))
+    assert torch.allclose(K.turn(r, -ang, "half"), q)
+    rot = dict(base=100.0, dims=8, scaling=dict(factor=2.0, original=64, fast=4.0, slow=0.5))
+    angs, amp = K.ramped_angles(3, rot)
+    f = angs[1]
+    plain = torch.tensor([100.0 ** (-2 * i / 8) for i in range(4)], dtype=D)
+    assert amp == pytest.approx(0.1 * math.log(2.0) + 1) and f[0] == plain[0] and torch.allclose(f[3], plain[3] / 2)
+    assert torch.allclose(f[1], plain[1] * (1 - 1 / 3) + plain[1] / 2 / 3)
+    m = K.window_mask(6, 3)
+    assert m[5].tolist() == [False, False, False, True, True, True] and m[1].tolist() == [True, True, False, False, False, False]
+    assert K.window_mask(3, 0).tolist() == [[True, False, False], [True, True, False], [True, True, True]]
+    # one channel: the state is a weighted sum of the candidates, each weight the product of the later keep factors
+    Wg = {"z": torch.tensor([[1.0]], dtype=D), "z.b": torch.tensor([0.3], dtype=D), "x": torch.tensor([[2.0]], dtype=D),
+          "x.b": torch.tensor([-0.5], dtype=D), "g": torch.tensor([[1.5]], dtype=D), "o": torch.tensor([[1.0]], dtype=D)}
+    h = torch.randn(5, 1, generator=g, dtype=D)
+    got = K.mingru(h, Wg, "")
+    z = torch.sigmoid(h[:, 0] + 0.3)
+    u = 2 * h[:, 0] - 0.5
+    cand = [float(v + 0.5) if v >= 0 else 1 / (1 + math.exp(-float(v))) for v in u]
+    assert any(v >= 0 for v in u) and any(v < 0 for v in u)
+    for t in range(5):
+        st = sum(float(z[j]) * cand[j] * math.prod(1 - float(z[i]) for i in range(j + 1, t + 1)) for j in range(t + 1))
+        assert float(got[t, 0]) == pytest.approx(st * float(K.silu(1.5 * h[t, 0])))
+    # two tokens, one head, no rotation on q and k, unit values: the second output sums two sigmoids and need not be below one
+    Wa = {"q": torch.zeros(2, 1, dtype=D), "q.b": torch.tensor([1.0, 0.0], dtype=D), "k": torch.zeros(2, 1, dtype=D), "k.b": torch.tensor([1.0, 0.0], dtype=D),
+          "v": torch.zeros(2, 1, dtype=D), "v.b": torch.tensor([1.0, 0.0], dtype=D), "q.norm": torch.ones(2, dtype=D), "k.norm": torch.ones(2, dtype=D),
+          "pb": torch.tensor([1.0], dtype=D), "g": torch.zeros(1, 1, dtype=D), "o": torch.eye(2, dtype=D), "o.b": torch.zeros(2, dtype=D)}
+    mx = dict(heads=1, kv_heads=1, dim=2, vdim=2, scale=0.5, rot=dict(base=100.0, dims=0))
+    out = K.sigmoid_attention(torch.zeros(2, 1, dtype=D), mx, Wa, "", 0.0)
+    wgt = 1 / (1 + math.exp(-(2.0 * 0.5 + 1.0)))          # normed q and k are (sqrt 2, 0): their product is 2
+    assert float(out[0, 0]) == pytest.approx(0.5 * wgt)
+    # the value at position 0 is not turned, the one at position 1 by the angle 1; the sum is turned back by 1
+    want1 = 0.5 * (wgt * math.cos(-1.0) + wgt)
+    assert float(out[1, 0]) == pytest.approx(want1) and 2 * wgt > 1.0
+    assert float(K.sigmoid_attention(torch.zeros(2, 1, dtype=D), dict(mx, mask=dict(size=1)), Wa, "", 0.0)[1, 0]) == pytest.approx(0.5 * wgt)
+    Wf = {"gate": torch.tensor([[1.0]], dtype=D), "up": torch.tensor([[1.0]], dtype=D), "down": torch.tensor([[1.0]], dtype=D)}
+    hv = torch.tensor([[-5.0], [0.5], [5.0]], dtype=D)
+    y = K.clamped_glu(hv, dict(limit=2.0), Wf, "")
+    assert float(y[2, 0]) == pytest.approx(2.0 / (1 + math.exp(-1.702 * 2.0)) * 3.0)
+    assert float(y[1, 0]) == pytest.approx(0.5 / (1 + math.exp(-1.702 * 0.5)) * 1.5)
+    assert float(y[0, 0]) == pytest.approx(-5.0 / (1 + math.exp(1.702 * 5.0)) * -1.0)
