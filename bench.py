@@ -14,6 +14,7 @@ Workloads (BASELINE.json configs):
   nekodra, musilorn: not BASELINE.json configs: prefill and decode tokens/s of the Nekodra / Musilorn family
         (include/b200_serve.h, random weights, --size s|m) beside the LLaMA engine at equal size; a line of its own shape.
   tomalix: the same for the Tomalix family, beside the Musilorn family at equal size.
+  sakevik: the same for the Sakevik family, beside the Tomalix family at equal size.
   cfg3: prefill, batch 4 x 2048 prompt tokens per GPU (metric prefill_tokens_per_s; a step = one prompt
         pass of the whole model: tcgen05 GEMMs + flash context attention; roofline = tensor).
 `value`  : tokens/s with everything resident in HBM, CUDA events on the engine's stream, max over ranks.
@@ -47,9 +48,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "nekodra", "musilorn", "tomalix"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "nekodra", "musilorn", "tomalix", "sakevik"])
     ap.add_argument("--size", default="m", choices=["s", "m"],
-                    help="nekodra / musilorn / tomalix: model shape (llm-inference_b200/bench_families.py SIZES, MUSILORN_SIZES, TOMALIX_SIZES)")
+                    help="nekodra / musilorn / tomalix / sakevik: model shape (llm-inference_b200/bench_families.py SIZES, MUSILORN_SIZES, TOMALIX_SIZES, SAKEVIK_SIZES)")
     ap.add_argument("--prompt", type=int, default=2048, help="nekodra: prompt tokens of the prefill measurement")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="cfg5: fused one-shot NVLink allreduce (product) or ncclAllReduce + AddResidual (baseline)")
@@ -905,8 +906,8 @@ def extras_multi_gpu(pkg, args, rank, world, local_rank, peak):
 # the B200 arm
 # --------------------------------------------------------------------------------------------
 def bench_family(args):
-    """--workload nekodra | musilorn | tomalix: prefill and decode tokens/s of that family (include/b200_serve.h) beside the LLaMA
-    engine (tomalix: beside the Musilorn family) at equal size; one JSON line of its own shape (the default workload's line and contract are untouched)."""
+    """--workload nekodra | musilorn | tomalix | sakevik: prefill and decode tokens/s of that family (include/b200_serve.h) beside the LLaMA
+    engine (tomalix: beside the Musilorn family; sakevik: beside the Tomalix family) at equal size; one JSON line of its own shape (the default workload's line and contract are untouched)."""
     from __graft_entry__ import load_package
     pkg = load_package()
     from llm_inference_b200 import bench_families
@@ -918,7 +919,7 @@ def bench_family(args):
 
 def main():
     args = parse()
-    if args.workload in ("nekodra", "musilorn", "tomalix"):
+    if args.workload in ("nekodra", "musilorn", "tomalix", "sakevik"):
         return bench_family(args)
     wl = workload(args)
     rank = int(os.environ.get("RANK", "0"))

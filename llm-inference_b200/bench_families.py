@@ -43,6 +43,26 @@ TOMALIX_SIZES = {
 }
 
 
+def sakevik_layers(width, heads, kv_heads, dim, ff, window, kv_rank, rot_dim, **_):
+    """four layers: a gated recurrence twice as wide as the model, without a feed-forward; windowed sigmoid attention with
+    rotated values; windowed latent attention with a rotated key part; the sigmoid attention again; the last three with a
+    clamped gated feed-forward"""
+    return [
+        dict(type="mingru", width=2 * width, ff=None),
+        dict(type="attention", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, window=window, ff=(ff, 7.0)),
+        dict(type="latent_attention", heads=heads, dim=dim, rot_dim=rot_dim, vdim=dim, kv_rank=kv_rank, window=window, ff=(ff, 7.0)),
+        dict(type="attention", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, window=window, ff=(ff, 7.0)),
+    ]
+
+
+# ff: a gated unit holds three matrices where the squared-relu unit of Tomalix holds two, so two thirds of its hidden width
+# (rounded to 128) give the same feed-forward weights per layer
+SAKEVIK_SIZES = {
+    "s": dict(width=1024, heads=8, kv_heads=4, dim=128, ff=2688, window=1024, kv_rank=256, rot_dim=64, n_layers=4, vocab=32000),
+    "m": dict(width=2048, heads=16, kv_heads=8, dim=128, ff=5504, window=1024, kv_rank=512, rot_dim=64, n_layers=4, vocab=32000),
+}
+
+
 def timed(fn, steps, warmup):
     import torch
     for _ in range(warmup):
@@ -62,6 +82,8 @@ def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, d
     S, E, capi = pkg.serve, pkg.engine, pkg.capi
     if family == "tomalix":
         return run_tomalix(pkg, size, prompt, batch, context, steps, warmup, dtype)
+    if family == "sakevik":
+        return run_sakevik(pkg, size, prompt, batch, context, steps, warmup, dtype)
     sz = (MUSILORN_SIZES if family == "musilorn" else SIZES)[size]
     rng = np.random.default_rng(0)
     out = {"workload": family, "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
@@ -175,4 +197,27 @@ def run_tomalix(pkg, size, prompt, batch, context, steps, warmup, dtype):
         out["musilorn_equal_size"] = res
     except Exception as ex:   # the comparison must not take the family's own numbers down
         out["musilorn_equal_size"] = {"failed": f"{type(ex).__name__}: {ex}"}
+    return out
+
+
+def run_sakevik(pkg, size, prompt, batch, context, steps, warmup, dtype):
+    """The Sakevik family beside the closest existing one, Tomalix (the same serving layer and fp32 residual; gated attention
+    with a mask, a recurrence with carried state, dense feed-forwards), at equal width, heads, head size, layer count,
+    vocabulary and feed-forward weights per layer."""
+    S = pkg.serve
+    sz = SAKEVIK_SIZES[size]
+    out = {"workload": "sakevik", "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
+           "dtype": dtype, "data": "synthetic ids, random weights", "timing": "host clock around synchronous steps (each step ends "
+           "with the device-to-host copy of its results), after warm-up"}
+    cfg, w = S.random_sakevik(sz["width"], sz["vocab"], sakevik_layers(**sz))
+    out.update(serve_family(S, cfg, w, prompt, batch, context, steps, warmup, dtype, sz["vocab"]))
+    del w
+    tx = dict(TOMALIX_SIZES[size])
+    try:
+        cfg, w = S.random_tomalix(tx["width"], tx["vocab"], tomalix_layers(**tx))
+        res = serve_family(S, cfg, w, prompt, batch, context, steps, warmup, dtype, tx["vocab"])
+        res["shape"] = tx
+        out["tomalix_equal_size"] = res
+    except Exception as ex:   # the comparison must not take the family's own numbers down
+        out["tomalix_equal_size"] = {"failed": f"{type(ex).__name__}: {ex}"}
     return out

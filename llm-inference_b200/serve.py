@@ -446,3 +446,55 @@ def random_tomalix(width, vocab, layers, loop=None, seed=0):
                 w[pre + "mlp.router"], w[pre + "mlp.router.b"] = rnd(E, width), torch.zeros(E)
         cfg["layers"].append(dict(type=kind, mixer=mx, mlp=ml))
     return cfg, w
+
+
+def random_sakevik(width, vocab, layers, buckets=65521, seed=0):
+    """(config, tensors) of a random Sakevik model. layers: dicts with type 'mingru' (width) | 'attention' (heads, kv_heads,
+    dim, vdim, window) | 'latent_attention' (heads, dim, rot_dim, vdim, kv_rank, window); ff = None | (ff, limit)"""
+    import math
+
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, s=None):
+        return (torch.randn(*shape, generator=g) * (s if s is not None else 1.0 / math.sqrt(shape[-1]))).to(torch.bfloat16)
+
+    cfg = dict(architecture="Sakevik", vocab=vocab, width=width, norm=dict(eps=1e-6), logit_scale=0.5,
+               embedding=dict(scale=math.sqrt(width), bigram=dict(buckets=buckets, mul_prev=31, mul_cur=17)), layers=[])
+    w = {"embed": rnd(vocab, width), "bigram": rnd(buckets + 1, width, s=0.5), "head": rnd(vocab, width), "final.norm": torch.ones(width)}
+    for i, sp in enumerate(layers):
+        pre, mp = f"l{i}.", f"l{i}.mix."
+        w[pre + "norm1"] = torch.ones(width)
+        if sp["type"] == "mingru":
+            C_ = sp["width"]
+            mx = dict(width=C_)
+            w[mp + "z"], w[mp + "x"], w[mp + "g"], w[mp + "o"] = rnd(C_, width), rnd(C_, width), rnd(C_, width), rnd(width, C_)
+            w[mp + "z.b"], w[mp + "x.b"] = torch.zeros(C_), torch.zeros(C_)
+        elif sp["type"] == "attention":
+            H, G, d, dv = sp["heads"], sp["kv_heads"], sp["dim"], sp["vdim"]
+            mx = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=1.0 / math.sqrt(d), rot=dict(base=10000.0, dims=d))
+            if sp.get("window"):
+                mx["mask"] = dict(size=sp["window"])
+            for nm, rows in (("q", H * d), ("k", G * d), ("v", G * dv)):
+                w[mp + nm], w[mp + nm + ".b"] = rnd(rows, width), torch.zeros(rows)
+            w[mp + "q.norm"], w[mp + "k.norm"], w[mp + "pb"] = torch.ones(d), torch.ones(d), torch.full((H,), -4.0)
+            w[mp + "g"], w[mp + "o"], w[mp + "o.b"] = rnd(H, width), rnd(width, H * dv), torch.zeros(width)
+        else:
+            H, d, dr, dv, R = sp["heads"], sp["dim"], sp["rot_dim"], sp["vdim"], sp["kv_rank"]
+            mx = dict(heads=H, dim=d, rot_dim=dr, vdim=dv, kv_rank=R, scale=1.0 / math.sqrt(d + dr),
+                      rot=dict(base=500000.0, dims=dr, scaling=dict(factor=8.0, original=8192, fast=32.0, slow=1.0)))
+            if sp.get("window"):
+                mx["mask"] = dict(size=sp["window"])
+            w[mp + "q"], w[mp + "dkv"], w[mp + "dkv.norm"] = rnd(H * (d + dr), width), rnd(R + dr, width), torch.ones(R)
+            w[mp + "uk"], w[mp + "uv"], w[mp + "o"] = rnd(H * d, R), rnd(H * dv, R), rnd(width, H * dv)
+        ff = sp.get("ff")
+        if ff is None:
+            ml = None
+        else:
+            f, lim = ff
+            ml = dict(kind="dense", ff=f, limit=lim)
+            w[pre + "norm2"] = torch.ones(width)
+            w[pre + "mlp.gate"], w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(f, width), rnd(f, width), rnd(width, f)
+        cfg["layers"].append(dict(type=sp["type"], mixer=mx, mlp=ml))
+    return cfg, w
