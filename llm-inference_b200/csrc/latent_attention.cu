@@ -28,7 +28,7 @@
 
 namespace b200 {
 
-constexpr int kMaxRankPerLane = 16;   // rank <= 512
+constexpr int kMaxRankPerLane = 20;   // rank <= 640 (a latent of 512 with a rotated part of 64 or 128)
 
 template <typename T>
 __global__ void __launch_bounds__(128) latent_store_kernel(const float* __restrict__ raw, long long ld_raw,
@@ -177,7 +177,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 }
 
 template <int NT>   // n8 column tiles of the output per warp: padded rank <= 64 * NT
-__global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* __restrict__ qa, float* __restrict__ out,
+__global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(const float* __restrict__ qa, float* __restrict__ out,
                                                                const __nv_bfloat16* __restrict__ pool, const int* __restrict__ pages,
                                                                int max_pages, int page_rows, const int* __restrict__ slot,
                                                                const int* __restrict__ pos, const float* __restrict__ sink, float scale,
@@ -515,7 +515,8 @@ extern "C" int b200_latent_attention_ex(const b200_latent_attention_args* ap, vo
         if (ntw <= 1) return go(latent_attn_tile_kernel<1>);
         if (ntw <= 2) return go(latent_attn_tile_kernel<2>);
         if (ntw <= 4) return go(latent_attn_tile_kernel<4>);
-        return go(latent_attn_tile_kernel<8>);
+        if (ntw <= 8) return go(latent_attn_tile_kernel<8>);
+        return go(latent_attn_tile_kernel<10>);
     }
     if (dtype == B200_BF16)
         latent_attn_kernel<__nv_bfloat16><<<grid, 128, smem, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows,

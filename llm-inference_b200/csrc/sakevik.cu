@@ -215,7 +215,7 @@ int Sakevik::load(const ModelDir& dir, const b200_model_options& opt, std::strin
                     err = where + "rot: dims must equal rot_dim, base above 1";
                     return B200_EINVAL;
                 }
-                if (L.rank + L.rot_dim > 512) { err = where + "cached rows wider than 512 are not supported by the latent attention kernels"; return B200_EUNSUPPORTED; }
+                if (L.rank + L.rot_dim > 640) { err = where + "cached rows wider than 640 are not supported by the latent attention kernels"; return B200_EUNSUPPORTED; }
                 L.rot_dims = L.rot_dim;
                 L.n_in = L.heads * (L.dim + L.rot_dim) + L.rank + L.rot_dim;
             } else {

@@ -288,6 +288,7 @@ LAT_SHAPES = [  # heads, rank, extra, window
     (16, 128, 64, 0),     # no window
     (1, 3, 2, 1),
     (40, 24, 8, 70),      # more heads than a tile has rows
+    (4, 512, 64, 150),    # the widest rows the kernels take
 ]
 
 
