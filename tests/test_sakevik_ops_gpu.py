@@ -162,6 +162,7 @@ ATT_SHAPES = [  # heads, kv, dim, vdim, window
     (4, 4, 128, 128, 300),  # a window that reaches the split of long contexts
     (2, 2, 64, 64, 0),      # no window
     (1, 1, 4, 2, 1),        # a position that only sees itself
+    (6, 2, 16, 8, 400),     # three heads per key head: the row kernel, its long contexts split over CTAs
 ]
 
 
