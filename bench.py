@@ -907,7 +907,7 @@ def extras_multi_gpu(pkg, args, rank, world, local_rank, peak):
 # --------------------------------------------------------------------------------------------
 def bench_family(args):
     """--workload nekodra | musilorn | tomalix | sakevik: prefill and decode tokens/s of that family (include/b200_serve.h) beside the LLaMA
-    engine (tomalix: beside the Musilorn family; sakevik: beside the Tomalix family) at equal size; one JSON line of its own shape (the default workload's line and contract are untouched)."""
+    engine (tomalix: beside the Musilorn family; sakevik: beside the Tomalix family) at equal size; one JSON line of its own shape (the default workload and its line stay as they are)."""
     from __graft_entry__ import load_package
     pkg = load_package()
     from llm_inference_b200 import bench_families

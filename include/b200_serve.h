@@ -116,6 +116,7 @@ typedef struct b200_latent_attention_args {
     int window;
     int dtype, longest_entry, longest_context;
     void* workspace; size_t workspace_bytes;
+    int out_cols;                    /* > 0: only out[t, h, 0:out_cols] is formed (the latent part of the rows); 0: all   */
 } b200_latent_attention_args;
 int b200_latent_attention_ex(const b200_latent_attention_args* a, void* stream);
 /* Latent cache rows with a rotated part: row = [norm(raw[t, 0:rank]) * w | rot(raw[t, rank:rank+extra])], the rotation by

@@ -182,7 +182,10 @@ __global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(
                                                                int max_pages, int page_rows, const int* __restrict__ slot,
                                                                const int* __restrict__ pos, const float* __restrict__ sink, float scale,
                                                                int n_tokens, int heads, int rank, int HG, int TQ, int splits,
-                                                               float* __restrict__ part, int window) {
+                                                               float* __restrict__ part, int window, int out_cols, int single) {
+    // out_cols: the weighted sum is formed for the first out_cols columns of a row only (a caller that uses the latent part
+    // of [latent | rotated part] rows). single: one half-tile buffer instead of two (rows wider than 512: two CTAs still
+    // share an SM, and the other CTA's arithmetic covers this one's load)
     // splits > 1 (blockIdx.z): this CTA walks one share of the key tiles and leaves (m, l, unnormalised O) per row in
     // `part` [token, head, split, 2 + rank]; latent_attn_combine_kernel merges the shares and the sink
     using bf = __nv_bfloat16;
@@ -190,7 +193,7 @@ __global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(
     const int rpad = (rank + 15) & ~15, RS = rpad + 8;           // smem row stride in elements (16-byte multiple)
     bf* Qs = reinterpret_cast<bf*>(smraw);                        // [32][RS]
     bf* Ks = Qs + kTileRows * RS;                                 // [2][32][RS]: half tiles, one being filled while the other is used
-    float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * RS);    // [2][32][36]: partial scores of the two halves of the rank
+    float* Ss = reinterpret_cast<float*>(Ks + (single ? kHalfKeys : kTileKeys) * RS);    // [2][32][36]: partial scores of the two halves of the rank
     bf* Ps = reinterpret_cast<bf*>(Ss);                           // [32][72]: a row's probabilities overwrite its own scores
     float* alpha_s = Ss + 2 * kTileRows * 36;                     // [32]
     float* linv_s = alpha_s + kTileRows;                          // [32]
@@ -199,7 +202,7 @@ __global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gid = lane / 4, tig = lane % 4;
     const int t0 = blockIdx.x * TQ, h0 = blockIdx.y * HG;
     const int ntok = min(TQ, n_tokens - t0);
-    const int n8 = rpad / 8;                                      // n8 tiles of the output
+    const int n8 = ((out_cols + 15) & ~15) / 8;                   // n8 tiles of the output
     const int ntw = (n8 + kTileWarps - 1) / kTileWarps;           // per warp (<= NT)
     const int tile0 = warp * ntw;
 
@@ -273,13 +276,17 @@ __global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(
         // the rank is split between the warp groups 0-3 and 4-7 in the score phase (k steps of 16)
         const int ksplit = (rpad / 32) * 16;
         const int kbeg = warp < 4 ? 0 : ksplit, kend = warp < 4 ? ksplit : rpad;
-        if (key_lo < n_keys) load_half(key_lo, Ks);
+        if (!single && key_lo < n_keys) load_half(key_lo, Ks);
         int buf = 0;
-        for (int k0 = key_lo; k0 < n_keys; k0 += kHalfKeys, buf ^= 1) {
+        for (int k0 = key_lo; k0 < n_keys; k0 += kHalfKeys, buf ^= single ? 0 : 1) {
             bf* Kb = Ks + buf * kHalfKeys * RS;
+            if (single) {
+                __syncthreads();   // the buffer, Ss and Ps are no longer read
+                load_half(k0, Ks);
+            }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();   // half k0 has landed for everybody; the other buffer, Ss and Ps are no longer read
-            if (k0 + kHalfKeys < n_keys) load_half(k0 + kHalfKeys, Ks + (buf ^ 1) * kHalfKeys * RS);
+            if (!single && k0 + kHalfKeys < n_keys) load_half(k0 + kHalfKeys, Ks + (buf ^ 1) * kHalfKeys * RS);
             {   // ---- partial scores: keys [8 (warp & 3), +8), rank columns [kbeg, kend)
                 float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 const bf* krow = Kb + ((warp & 3) * 8 + gid) * RS + tig * 2;
@@ -377,8 +384,8 @@ __global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(
                     const int tile = tile0 + nt;
                     if (nt < ntw && tile < n8) {
                         const int c = tile * 8 + tig * 2;
-                        if (c < rank) dst[c] = o[mt][nt][half * 2] * inv;
-                        if (c + 1 < rank) dst[c + 1] = o[mt][nt][half * 2 + 1] * inv;
+                        if (c < out_cols) dst[c] = o[mt][nt][half * 2] * inv;
+                        if (c + 1 < out_cols) dst[c + 1] = o[mt][nt][half * 2 + 1] * inv;
                     }
                 }
             }
@@ -388,7 +395,7 @@ __global__ void __launch_bounds__(256, NT <= 8 ? 2 : 1) latent_attn_tile_kernel(
 
 // merges the shares of a split launch: grid (token, head)
 __global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
-                                                                  const float* __restrict__ sink, int heads, int rank, int splits) {
+                                                                  const float* __restrict__ sink, int heads, int rank, int splits, int out_cols) {
     const int t = blockIdx.x, h = blockIdx.y;
     const float* p = part + ((size_t)t * heads + h) * splits * (rank + 2);
     const float sk = sink ? sink[h] : -INFINITY;
@@ -397,7 +404,7 @@ __global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* _
     float den = expf(sk - M);
     for (int z = 0; z < splits; ++z) den += p[(size_t)z * (rank + 2) + 1] * expf(p[(size_t)z * (rank + 2)] - M);
     const float inv = 1.0f / den;
-    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    for (int c = threadIdx.x; c < out_cols; c += blockDim.x) {
         float acc = 0.f;
         for (int z = 0; z < splits; ++z) acc += p[(size_t)z * (rank + 2) + 2 + c] * expf(p[(size_t)z * (rank + 2)] - M);
         out[((size_t)t * heads + h) * rank + c] = acc * inv;
@@ -464,7 +471,7 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
                                      void* workspace, size_t workspace_bytes, void* stream) {
     if (!sink) return B200_EINVAL;
     b200_latent_attention_args a{qa, out, pool, pages, max_pages, page_rows, slot, pos, sink, scale, n_tokens, heads, rank, 0, dtype,
-                                 longest_entry, longest_context, workspace, workspace_bytes};
+                                 longest_entry, longest_context, workspace, workspace_bytes, 0};
     return b200_latent_attention_ex(&a, stream);
 }
 
@@ -476,6 +483,7 @@ extern "C" int b200_latent_attention_ex(const b200_latent_attention_args* ap, vo
     const int n_tokens = ap->n_tokens, heads = ap->heads, rank = ap->rank, window = ap->window, dtype = ap->dtype, longest_entry = ap->longest_entry;
     const int longest_context = window > 0 && ap->longest_context > 0 ? std::min(ap->longest_context, window + kTileKeys) : ap->longest_context;
     void* workspace = ap->workspace; const size_t workspace_bytes = ap->workspace_bytes;
+    const int out_cols = ap->out_cols > 0 && ap->out_cols < rank ? ap->out_cols : rank;
     if (!qa || !out || !pool || !pages || !slot || !pos || n_tokens < 0 || heads < 1 || rank < 1 || window < 0) return B200_EINVAL;
     if (rank > 32 * kMaxRankPerLane || heads > 65535) return B200_EUNSUPPORTED;
     if (n_tokens == 0) return B200_OK;
@@ -487,8 +495,9 @@ extern "C" int b200_latent_attention_ex(const b200_latent_attention_args* ap, vo
         // every entry a single token (a decode batch): one token per CTA, its heads the only rows
         const int HG = heads < kTileRows ? heads : kTileRows, TQ = longest_entry == 1 ? 1 : kTileRows / HG;
         const int rpad = (rank + 15) & ~15, RS = rpad + 8;
-        const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + 2 * kTileRows * 36 * 4 + 3 * kTileRows * 4;
-        const int ntw = (rpad / 8 + kTileWarps - 1) / kTileWarps;
+        const int single = rpad > 512;   // with one half-tile buffer two CTAs of such rows still fit an SM
+        const size_t tsm = (size_t)(kTileRows + (single ? kHalfKeys : kTileKeys)) * RS * 2 + 2 * kTileRows * 36 * 4 + 3 * kTileRows * 4;
+        const int ntw = ((((out_cols + 15) & ~15) / 8) + kTileWarps - 1) / kTileWarps;
         dim3 tg((n_tokens + TQ - 1) / TQ, (heads + HG - 1) / HG);
         // few CTAs over long contexts (decoding): shares of the key tiles on blockIdx.z, merged by the combine kernel
         int splits = 1;
@@ -500,23 +509,24 @@ extern "C" int b200_latent_attention_ex(const b200_latent_attention_args* ap, vo
         }
         tg.z = splits;
         float* part = reinterpret_cast<float*>(workspace);
-        auto go = [&](auto kern) -> int {
-            static unsigned long long done = 0;
-            if (tsm > 48 * 1024 && ensure_max_dynamic_smem((const void*)kern, 200 * 1024, done) != cudaSuccess) return B200_EUNSUPPORTED;
+        // every instantiation has the same function type, so the lambda is ONE function: a mask per kernel, not one static
+        auto go = [&](auto kern, int which) -> int {
+            static unsigned long long done[5] = {0, 0, 0, 0, 0};
+            if (tsm > 48 * 1024 && ensure_max_dynamic_smem((const void*)kern, 200 * 1024, done[which]) != cudaSuccess) return B200_EUNSUPPORTED;
             kern<<<tg, 256, tsm, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows, slot, pos, sink, scale, n_tokens,
-                                      heads, rank, HG, TQ, splits, part, window);
+                                      heads, rank, HG, TQ, splits, part, window, out_cols, single);
             count_launch();
             if (splits > 1) {
-                latent_attn_combine_kernel<<<dim3(n_tokens, heads), 128, 0, s>>>(part, out, sink, heads, rank, splits);
+                latent_attn_combine_kernel<<<dim3(n_tokens, heads), 128, 0, s>>>(part, out, sink, heads, rank, splits, out_cols);
                 count_launch();
             }
             return (int)cudaGetLastError();
         };
-        if (ntw <= 1) return go(latent_attn_tile_kernel<1>);
-        if (ntw <= 2) return go(latent_attn_tile_kernel<2>);
-        if (ntw <= 4) return go(latent_attn_tile_kernel<4>);
-        if (ntw <= 8) return go(latent_attn_tile_kernel<8>);
-        return go(latent_attn_tile_kernel<10>);
+        if (ntw <= 1) return go(latent_attn_tile_kernel<1>, 0);
+        if (ntw <= 2) return go(latent_attn_tile_kernel<2>, 1);
+        if (ntw <= 4) return go(latent_attn_tile_kernel<4>, 2);
+        if (ntw <= 8) return go(latent_attn_tile_kernel<8>, 3);
+        return go(latent_attn_tile_kernel<10>, 4);
     }
     if (dtype == B200_BF16)
         latent_attn_kernel<__nv_bfloat16><<<grid, 128, smem, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows,

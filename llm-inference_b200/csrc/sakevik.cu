@@ -523,6 +523,7 @@ int Sakevik::enqueue(int T, int W, int longest_entry, int longest_context, bool 
             la.n_tokens = T; la.heads = H; la.rank = row; la.window = L.window; la.dtype = dt;
             la.longest_entry = longest_entry; la.longest_context = longest_context;
             la.workspace = attn_ws_; la.workspace_bytes = attn_ws_bytes_;
+            la.out_cols = R;   // the value up-projection reads the latent columns only
             SK_OP(b200_latent_attention_ex(&la, stream_));
             {   // mid[t, h, :] = W_uv,h oa[t, h, 0:R]
                 b200_gemm_grouped_args g{};

@@ -81,7 +81,7 @@ class LatentAttentionArgs(C.Structure):
     _fields_ = [("qa", _vp), ("out", _vp), ("pool", _vp), ("pages", _vp), ("max_pages", _i), ("page_rows", _i),
                 ("slot", _vp), ("pos", _vp), ("sink", _vp), ("scale", _f), ("n_tokens", _i), ("heads", _i), ("rank", _i),
                 ("window", _i), ("dtype", _i), ("longest_entry", _i), ("longest_context", _i),
-                ("workspace", _vp), ("workspace_bytes", _sz)]
+                ("workspace", _vp), ("workspace_bytes", _sz), ("out_cols", _i)]
 
 
 class GatedRecurrenceArgs(C.Structure):

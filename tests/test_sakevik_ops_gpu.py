@@ -326,14 +326,15 @@ def test_windowed_latent_attention_without_a_sink(S, shape, kind):
     if win > 1:
         assert want[50, 0, 1] > 2.5 and want[50, 0, 1] < 3.5
 
-    def run(qq, sl, ps, longest):
+    def run(qq, sl, ps, longest, out_cols=0):
         T = len(sl)
         out = torch.zeros(T, H, W, device="cuda")
         need = S.lib().b200_latent_attention_workspace_bytes(T, H, W)
         ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
         _alive.extend([out, ws])
         a = S.LatentAttentionArgs(dev(qq, torch.float32).data_ptr(), out.data_ptr(), pool.data_ptr(), table.data_ptr(), max_pages, PR,
-                                  ints(sl).data_ptr(), ints(ps).data_ptr(), None, scale, T, H, W, win, code, longest, max(ps) + 1, ws.data_ptr(), need)
+                                  ints(sl).data_ptr(), ints(ps).data_ptr(), None, scale, T, H, W, win, code, longest, max(ps) + 1, ws.data_ptr(), need,
+                                  out_cols)
         sync_ok(S.lib().b200_latent_attention_ex(C.byref(a), None))
         return out
 
@@ -341,6 +342,9 @@ def test_windowed_latent_attention_without_a_sink(S, shape, kind):
     assert rel(run(qa, slot, pos, new0), want) < tol
     pick = [50, new0 - 1, new0]
     assert rel(run(qa[pick], [slot[i] for i in pick], [pos[i] for i in pick], 1), want[pick]) < tol
+    # a caller that only uses the latent columns of the weighted sum
+    assert rel(run(qa, slot, pos, new0, R)[:, :, :R], want[:, :, :R]) < tol
+    assert rel(run(qa[pick], [slot[i] for i in pick], [pos[i] for i in pick], 1, R)[:, :, :R], want[pick][:, :, :R]) < tol
 
 
 @pytest.mark.parametrize("kind", ["f32", "bf16"])
